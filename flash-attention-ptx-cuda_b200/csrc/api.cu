@@ -1,0 +1,236 @@
+// Entry points of libfa_b200.so that do not own a kernel: argument validation
+// and dispatch for prefill, the host-buffer convenience call, device status,
+// and the C++ shim transformer::launch_flash_attention that keeps the reference
+// project's launch interface (include/flash_attention.h:51-67) working.
+#include <cmath>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+
+#include "../../include/flash_attention.h"
+#include "host_common.h"
+
+namespace fa {
+
+namespace {
+constexpr int kMaxDevices = 64;
+DeviceState g_states[kMaxDevices];
+std::mutex  g_mutex;
+thread_local char g_last_cuda_error[256] = "";
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn g_encode = nullptr;
+}  // namespace
+
+int note_cuda_error(cudaError_t err, const char* where) {
+    snprintf(g_last_cuda_error, sizeof(g_last_cuda_error), "%s: %s", where, cudaGetErrorString(err));
+    return FA_ERR_CUDA;
+}
+int note_driver_error(CUresult err, const char* where) {
+    snprintf(g_last_cuda_error, sizeof(g_last_cuda_error), "%s: CUresult %d", where, (int)err);
+    return FA_ERR_CUDA;
+}
+
+DeviceState* device_state() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
+    DeviceState* st = &g_states[dev];
+    if (st->device == dev) return st;
+    std::lock_guard<std::mutex> lock(g_mutex);
+    if (st->device == dev) return st;
+    int sms = 0, major = 0;
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return nullptr;
+    if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess) return nullptr;
+    int* status = nullptr;
+    if (cudaMalloc(&status, sizeof(int)) != cudaSuccess) return nullptr;
+    if (cudaMemset(status, 0, sizeof(int)) != cudaSuccess) return nullptr;
+    if (!g_encode) {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) != cudaSuccess ||
+            qres != cudaDriverEntryPointSuccess || !fn)
+            return nullptr;
+        g_encode = reinterpret_cast<EncodeTiledFn>(fn);
+    }
+    st->sm_count = sms;
+    st->cc_major = major;
+    st->status   = status;
+    st->device   = dev;
+    return st;
+}
+
+int make_tensor_map_3d(CUtensorMap* out, const void* base, int dtype, uint64_t row_elems,
+                       uint64_t n_rows, uint64_t n_heads, uint32_t box_cols, uint32_t box_rows) {
+    const uint64_t es = (dtype == FA_DTYPE_E4M3) ? 1 : 2;
+    const CUtensorMapDataType dt = (dtype == FA_DTYPE_E4M3)   ? CU_TENSOR_MAP_DATA_TYPE_UINT8
+                                   : (dtype == FA_DTYPE_BF16) ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                                              : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    cuuint64_t dims[3]    = {row_elems, n_rows, n_heads};
+    cuuint64_t strides[2] = {row_elems * es, row_elems * n_rows * es};
+    cuuint32_t box[3]     = {box_cols, box_rows, 1};
+    cuuint32_t estr[3]    = {1, 1, 1};
+    CUresult r = g_encode(out, dt, 3, const_cast<void*>(base), dims, strides, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                          CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return note_driver_error(r, "cuTensorMapEncodeTiled");
+    return FA_OK;
+}
+
+namespace {
+
+int validate_prefill(const fa_prefill_args* a) {
+    if (!a || !a->q || !a->k || !a->v || !a->o) return FA_ERR_INVALID_ARGUMENT;
+    if (a->batch_size <= 0 || a->num_heads <= 0 || a->seq_len <= 0) return FA_ERR_INVALID_ARGUMENT;
+    if (!(a->scale > 0.0f) || !std::isfinite(a->scale)) return FA_ERR_INVALID_ARGUMENT;
+    if ((long long)a->batch_size * a->num_heads > 0x7FFFFFFFll) return FA_ERR_INVALID_ARGUMENT;
+    if (a->dtype != FA_DTYPE_F16 && a->dtype != FA_DTYPE_BF16 && a->dtype != FA_DTYPE_E4M3)
+        return FA_ERR_UNSUPPORTED;
+    if (a->d_head != 64 && a->d_head != 128) return FA_ERR_UNSUPPORTED;
+    if (a->dtype == FA_DTYPE_E4M3) {
+        if (a->d_head != 128) return FA_ERR_UNSUPPORTED;
+        if (!a->q_scale || !a->k_scale || !a->v_scale) return FA_ERR_INVALID_ARGUMENT;
+    }
+    return FA_OK;
+}
+
+// Grows staging buffer `slot` of the current device to at least `bytes`.
+int stage_reserve(DeviceState* st, int slot, size_t bytes) {
+    if (st->stage_bytes[slot] >= bytes) return FA_OK;
+    if (st->stage[slot]) FA_CUDA_TRY(cudaFree(st->stage[slot]));
+    st->stage[slot] = nullptr;
+    st->stage_bytes[slot] = 0;
+    FA_CUDA_TRY(cudaMalloc(&st->stage[slot], bytes));
+    st->stage_bytes[slot] = bytes;
+    return FA_OK;
+}
+
+}  // namespace
+}  // namespace fa
+
+using namespace fa;
+
+FA_EXPORT int fa_prefill(const fa_prefill_args* a) {
+    int rc = validate_prefill(a);
+    if (rc != FA_OK) return rc;
+    if (!aligned16(a->q) || !aligned16(a->k) || !aligned16(a->v) || !aligned16(a->o))
+        return FA_ERR_MISALIGNED;
+    if (a->lse && (reinterpret_cast<uintptr_t>(a->lse) & 3u)) return FA_ERR_MISALIGNED;
+    DeviceState* st = device_state();
+    if (!st) return FA_ERR_CUDA;
+    if (st->cc_major != 10) return FA_ERR_NOT_SM100;
+    if (a->dtype == FA_DTYPE_E4M3) return launch_prefill_fp8(*a, st);
+    return launch_prefill_16bit(*a, st);
+}
+
+FA_EXPORT int fa_prefill_host(const fa_prefill_args* h) {
+    int rc = validate_prefill(h);
+    if (rc != FA_OK) return rc;
+    DeviceState* st = device_state();
+    if (!st) return FA_ERR_CUDA;
+    const size_t bh    = (size_t)h->batch_size * h->num_heads;
+    const size_t elems = bh * h->seq_len * h->d_head;
+    const size_t in_b  = elems * (h->dtype == FA_DTYPE_E4M3 ? 1 : 2);
+    const size_t out_b = elems * 2;
+    const size_t lse_b = bh * h->seq_len * sizeof(float);
+    const size_t sc_b  = bh * sizeof(float);
+    // slots: 0 q, 1 k, 2 v, 3 o, 4 lse, 5..7 scales
+    for (int s = 0; s < 3; s++)
+        if ((rc = stage_reserve(st, s, in_b)) != FA_OK) return rc;
+    if ((rc = stage_reserve(st, 3, out_b)) != FA_OK) return rc;
+    if (h->lse && (rc = stage_reserve(st, 4, lse_b)) != FA_OK) return rc;
+    cudaStream_t stream = nullptr;
+    FA_CUDA_TRY(cudaMemcpyAsync(st->stage[0], h->q, in_b, cudaMemcpyHostToDevice, stream));
+    FA_CUDA_TRY(cudaMemcpyAsync(st->stage[1], h->k, in_b, cudaMemcpyHostToDevice, stream));
+    FA_CUDA_TRY(cudaMemcpyAsync(st->stage[2], h->v, in_b, cudaMemcpyHostToDevice, stream));
+    fa_prefill_args d = *h;
+    d.q = st->stage[0]; d.k = st->stage[1]; d.v = st->stage[2]; d.o = st->stage[3];
+    d.lse = h->lse ? static_cast<float*>(st->stage[4]) : nullptr;
+    d.stream = stream;
+    if (h->dtype == FA_DTYPE_E4M3) {
+        const float* src[3] = {h->q_scale, h->k_scale, h->v_scale};
+        for (int s = 0; s < 3; s++) {
+            if ((rc = stage_reserve(st, 5 + s, sc_b)) != FA_OK) return rc;
+            FA_CUDA_TRY(cudaMemcpyAsync(st->stage[5 + s], src[s], sc_b, cudaMemcpyHostToDevice, stream));
+        }
+        d.q_scale = static_cast<float*>(st->stage[5]);
+        d.k_scale = static_cast<float*>(st->stage[6]);
+        d.v_scale = static_cast<float*>(st->stage[7]);
+    }
+    if ((rc = fa_prefill(&d)) != FA_OK) return rc;
+    FA_CUDA_TRY(cudaMemcpyAsync(h->o, st->stage[3], out_b, cudaMemcpyDeviceToHost, stream));
+    if (h->lse) FA_CUDA_TRY(cudaMemcpyAsync(h->lse, st->stage[4], lse_b, cudaMemcpyDeviceToHost, stream));
+    FA_CUDA_TRY(cudaStreamSynchronize(stream));
+    int word = 0;
+    FA_CUDA_TRY(cudaMemcpy(&word, st->status, sizeof(int), cudaMemcpyDeviceToHost));
+    return word == 0 ? FA_OK : FA_ERR_DEVICE_TIMEOUT;
+}
+
+FA_EXPORT int fa_device_status(int* status_word) {
+    DeviceState* st = device_state();
+    if (!st) return FA_ERR_CUDA;
+    FA_CUDA_TRY(cudaDeviceSynchronize());
+    int word = 0;
+    FA_CUDA_TRY(cudaMemcpy(&word, st->status, sizeof(int), cudaMemcpyDeviceToHost));
+    if (status_word) *status_word = word;
+    return word == 0 ? FA_OK : FA_ERR_DEVICE_TIMEOUT;
+}
+
+FA_EXPORT int fa_clear_device_status(void) {
+    DeviceState* st = device_state();
+    if (!st) return FA_ERR_CUDA;
+    FA_CUDA_TRY(cudaDeviceSynchronize());
+    FA_CUDA_TRY(cudaMemset(st->status, 0, sizeof(int)));
+    return FA_OK;
+}
+
+FA_EXPORT const char* fa_error_string(int code) {
+    switch (code) {
+        case FA_OK:                   return "ok";
+        case FA_ERR_INVALID_ARGUMENT: return "invalid argument";
+        case FA_ERR_UNSUPPORTED:      return "unsupported d_head, dtype or split count";
+        case FA_ERR_MISALIGNED:       return "device pointer not 16-byte aligned";
+        case FA_ERR_WORKSPACE:        return "workspace missing or too small";
+        case FA_ERR_CUDA:             return "CUDA call failed";
+        case FA_ERR_DEVICE_TIMEOUT:   return "a kernel gave up on a bounded wait";
+        case FA_ERR_NOT_SM100:        return "device is not compute capability 10.x";
+        default:                      return "unknown error";
+    }
+}
+
+FA_EXPORT const char* fa_last_cuda_error(void) { return g_last_cuda_error; }
+FA_EXPORT int fa_version(void) { return 100; }
+
+// ---------------------------------------------------------------------------
+// The reference's C++ entry point.  Same contract as
+// kernels/flash_attention.cu:595-617: enqueue on params.stream, return without
+// synchronising; any failure prints to stderr and exits, as CUDA_CHECK does in
+// the reference (include/flash_attention.h:35-43).
+// ---------------------------------------------------------------------------
+namespace transformer {
+
+__attribute__((visibility("default")))
+void launch_flash_attention(const FlashAttentionParams& params) {
+    fa_prefill_args a;
+    std::memset(&a, 0, sizeof(a));
+    a.q = params.Q; a.k = params.K; a.v = params.V; a.o = params.O; a.lse = params.L;
+    a.batch_size = params.batch_size;
+    a.num_heads  = params.num_heads;
+    a.seq_len    = params.seq_len;
+    a.d_head     = params.d_head;
+    a.scale      = params.scale;
+    a.causal     = params.causal ? 1 : 0;
+    a.dtype      = params.dtype == 1 ? FA_DTYPE_BF16 : FA_DTYPE_F16;
+    a.stream     = params.stream;
+    const int rc = fa_prefill(&a);
+    if (rc != FA_OK) {
+        fprintf(stderr, "launch_flash_attention: %s%s%s\n", fa_error_string(rc),
+                rc == FA_ERR_CUDA ? ": " : "", rc == FA_ERR_CUDA ? fa_last_cuda_error() : "");
+        exit(EXIT_FAILURE);
+    }
+}
+
+}  // namespace transformer

@@ -1,0 +1,316 @@
+// Split-KV decode (one query row per head against a long KV cache) and the LSE
+// merge ("combine") kernel.
+//
+// The reference has no decode path; the definition is its attention
+// (src/demo.cu:28-70) evaluated for a single query row, every key visible.  At
+// one query row the work is one multiply-add per byte of K and V read, so the
+// kernels here are built around HBM traffic, not tensor cores:
+//
+//   decode_partial_kernel  grid (splits, batch*heads).  Each warp streams rows
+//     of K and V straight from global memory with 128-bit loads (a 16-lane group
+//     covers one 256-byte row at d_head 128, so every warp instruction reads
+//     whole rows, fully coalesced), keeps an online softmax (running max, sum,
+//     fp32 accumulator slice) per lane group in registers, and never touches
+//     shared memory until the per-CTA merge at the end.  Output per (head,
+//     split): a normalised fp32 partial O and its natural-log LSE.
+//   combine_kernel  merges partials by their LSEs,
+//       m = max lse_p, w_p = exp(lse_p - m), O = sum w_p O_p / sum w_p,
+//       LSE = m + log(sum w_p),
+//     converts to the 16-bit output type, and can also emit the fp32 result.
+//     The same kernel merges the per-GPU partials of KV-sequence-sharded decode
+//     (parts = ranks), reading the gathered buffer directly.
+#include <cfloat>
+#include <cmath>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "host_common.h"
+
+namespace fa {
+namespace {
+
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLn2   = 0.6931471805599453f;
+constexpr int   kDecodeWarps = 8;
+constexpr int   kUnroll = 4;            // row groups in flight per warp iteration
+
+__device__ __forceinline__ uint4 ld_stream_16(const void* p) {
+    uint4 r;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w)
+                 : "l"(p));
+    return r;
+}
+
+template <bool BF16>
+__device__ __forceinline__ float2 unpack2(uint32_t w) {
+    if constexpr (BF16) {
+        return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xFFFF0000u));
+    } else {
+        return __half22float2(*reinterpret_cast<const __half2*>(&w));
+    }
+}
+
+template <bool BF16>
+__device__ __forceinline__ void unpack8(const uint4& u, float (&f)[8]) {
+    float2 a = unpack2<BF16>(u.x), b = unpack2<BF16>(u.y), c = unpack2<BF16>(u.z), d = unpack2<BF16>(u.w);
+    f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y; f[4] = c.x; f[5] = c.y; f[6] = d.x; f[7] = d.y;
+}
+
+__device__ __forceinline__ float fast_ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+// Merges two online-softmax states (m in log2 units).
+__device__ __forceinline__ void merge_state(float& m, float& l, float (&acc)[8], float m2, float l2,
+                                            const float (&acc2)[8]) {
+    const float mn = fmaxf(m, m2);
+    const float c1 = fast_ex2(m - mn), c2 = fast_ex2(m2 - mn);
+    l = l * c1 + l2 * c2;
+#pragma unroll
+    for (int e = 0; e < 8; e++) acc[e] = acc[e] * c1 + acc2[e] * c2;
+    m = mn;
+}
+
+template <int D, bool BF16>
+__global__ void __launch_bounds__(kDecodeWarps * 32)
+decode_partial_kernel(const uint16_t* __restrict__ q, const uint16_t* __restrict__ k,
+                      const uint16_t* __restrict__ v, float* __restrict__ o_part,
+                      float* __restrict__ lse_part, int seq_len_kv, int n_splits, int keys_per_split,
+                      float scale_log2) {
+    constexpr int LPR = D / 8;           // lanes covering one row (8 elements = 16 bytes per lane)
+    constexpr int RPW = 32 / LPR;        // rows per warp-wide load
+    constexpr int STEP = kDecodeWarps * RPW;
+    const int split = blockIdx.x, bh = blockIdx.y;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int sub = lane / LPR;          // which row of the warp-wide load this lane reads
+    const int dsl = (lane % LPR) * 8;    // first of this lane's 8 head-dim elements
+    const int k_begin = split * keys_per_split;
+    const int k_end = min(seq_len_kv, k_begin + keys_per_split);
+
+    float qf[8];
+    {
+        const uint4 qu = *reinterpret_cast<const uint4*>(q + (size_t)bh * D + dsl);
+        unpack8<BF16>(qu, qf);
+#pragma unroll
+        for (int e = 0; e < 8; e++) qf[e] *= scale_log2;
+    }
+    const uint16_t* kb = k + ((size_t)bh * seq_len_kv) * D + dsl;
+    const uint16_t* vb = v + ((size_t)bh * seq_len_kv) * D + dsl;
+
+    float m = -1e30f, l = 0.0f, acc[8];
+#pragma unroll
+    for (int e = 0; e < 8; e++) acc[e] = 0.0f;
+
+    for (int base = k_begin; base < k_end; base += kUnroll * STEP) {
+        // This lane's rows of the iteration: r0, r0 + STEP, ... (kUnroll of them).
+        const int r0 = base + warp * RPW + sub;
+        uint4 ku[kUnroll], vu[kUnroll];
+        bool valid[kUnroll];
+#pragma unroll
+        for (int u = 0; u < kUnroll; u++) {
+            const int r = r0 + u * STEP;
+            valid[u] = r < k_end;
+            const size_t off = (size_t)(valid[u] ? r : k_begin) * D;
+            ku[u] = ld_stream_16(kb + off);
+            vu[u] = ld_stream_16(vb + off);
+        }
+        float s[kUnroll];
+#pragma unroll
+        for (int u = 0; u < kUnroll; u++) {
+            float kf[8];
+            unpack8<BF16>(ku[u], kf);
+            float d = 0.0f;
+#pragma unroll
+            for (int e = 0; e < 8; e++) d = fmaf(qf[e], kf[e], d);
+#pragma unroll
+            for (int o = 1; o < LPR; o <<= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
+            s[u] = valid[u] ? d : -INFINITY;
+        }
+        float mn = m;
+#pragma unroll
+        for (int u = 0; u < kUnroll; u++) mn = fmaxf(mn, s[u]);
+        const float corr = fast_ex2(m - mn);
+        m = mn;
+        l *= corr;
+#pragma unroll
+        for (int e = 0; e < 8; e++) acc[e] *= corr;
+#pragma unroll
+        for (int u = 0; u < kUnroll; u++) {
+            const float p = fast_ex2(s[u] - mn);
+            l += p;
+            float vf[8];
+            unpack8<BF16>(vu[u], vf);
+#pragma unroll
+            for (int e = 0; e < 8; e++) acc[e] = fmaf(p, vf[e], acc[e]);
+        }
+    }
+
+    // Merge the RPW lane groups of the warp (they hold the same d-slice of different rows).
+#pragma unroll
+    for (int o = LPR; o < 32; o <<= 1) {
+        float m2 = __shfl_xor_sync(0xffffffffu, m, o);
+        float l2 = __shfl_xor_sync(0xffffffffu, l, o);
+        float a2[8];
+#pragma unroll
+        for (int e = 0; e < 8; e++) a2[e] = __shfl_xor_sync(0xffffffffu, acc[e], o);
+        merge_state(m, l, acc, m2, l2, a2);
+    }
+    // Merge the warps of the CTA through shared memory.
+    __shared__ float sm_m[kDecodeWarps], sm_l[kDecodeWarps];
+    __shared__ float sm_acc[kDecodeWarps][D];
+    if (lane < LPR) {
+#pragma unroll
+        for (int e = 0; e < 8; e++) sm_acc[warp][dsl + e] = acc[e];
+        if (lane == 0) { sm_m[warp] = m; sm_l[warp] = l; }
+    }
+    __syncthreads();
+    if (threadIdx.x < D) {
+        const int d = threadIdx.x;
+        float mm = -1e30f;
+#pragma unroll
+        for (int w = 0; w < kDecodeWarps; w++) mm = fmaxf(mm, sm_m[w]);
+        float ll = 0.0f, a = 0.0f;
+#pragma unroll
+        for (int w = 0; w < kDecodeWarps; w++) {
+            const float c = fast_ex2(sm_m[w] - mm);
+            ll += sm_l[w] * c;
+            a += sm_acc[w][d] * c;
+        }
+        const size_t pidx = (size_t)bh * n_splits + split;
+        o_part[pidx * D + d] = ll > 0.0f ? a / ll : 0.0f;
+        if (d == 0) lse_part[pidx] = ll > 0.0f ? kLn2 * (mm + log2f(ll)) : -INFINITY;
+    }
+}
+
+// One CTA per output row, one thread per head-dim element.
+template <bool BF16>
+__global__ void combine_kernel(const float* __restrict__ o_parts, const float* __restrict__ lse_parts,
+                               int n_parts, long long part_stride_o, long long row_stride_o,
+                               long long part_stride_l, long long row_stride_l, int d_head,
+                               uint16_t* __restrict__ o, float* __restrict__ lse,
+                               float* __restrict__ o_f32) {
+    const int row = blockIdx.x, d = threadIdx.x;
+    const float* lp = lse_parts + (size_t)row * row_stride_l;
+    float m = -INFINITY;
+    for (int p = 0; p < n_parts; p++) m = fmaxf(m, lp[(size_t)p * part_stride_l]);
+    float wsum = 0.0f, a = 0.0f;
+    if (m > -INFINITY) {
+        const float* op = o_parts + (size_t)row * row_stride_o + d;
+        for (int p = 0; p < n_parts; p++) {
+            const float w = fast_ex2((lp[(size_t)p * part_stride_l] - m) * kLog2e);
+            wsum += w;
+            a = fmaf(w, op[(size_t)p * part_stride_o], a);
+        }
+    }
+    const float out = wsum > 0.0f ? a / wsum : 0.0f;
+    if (o != nullptr) {
+        uint16_t bits;
+        if constexpr (BF16) bits = __bfloat16_as_ushort(__float2bfloat16_rn(out));
+        else bits = __half_as_ushort(__float2half_rn(out));
+        o[(size_t)row * d_head + d] = bits;
+    }
+    if (o_f32 != nullptr) o_f32[(size_t)row * d_head + d] = out;
+    if (lse != nullptr && d == 0) lse[row] = wsum > 0.0f ? m + kLn2 * log2f(wsum) : -INFINITY;
+}
+
+int launch_combine(const float* o_parts, const float* lse_parts, int n_parts, long long pso,
+                   long long rso, long long psl, long long rsl, int rows, int d_head, void* o,
+                   float* lse, float* o_f32, int dtype, cudaStream_t stream) {
+    if (dtype == FA_DTYPE_BF16)
+        combine_kernel<true><<<rows, d_head, 0, stream>>>(o_parts, lse_parts, n_parts, pso, rso, psl, rsl,
+                                                          d_head, static_cast<uint16_t*>(o), lse, o_f32);
+    else
+        combine_kernel<false><<<rows, d_head, 0, stream>>>(o_parts, lse_parts, n_parts, pso, rso, psl, rsl,
+                                                           d_head, static_cast<uint16_t*>(o), lse, o_f32);
+    FA_CUDA_TRY(cudaGetLastError());
+    return FA_OK;
+}
+
+size_t align256(size_t x) { return (x + 255) & ~size_t(255); }
+
+}  // namespace
+}  // namespace fa
+
+using namespace fa;
+
+FA_EXPORT size_t fa_decode_workspace_bytes(int batch_size, int num_heads, int d_head, int num_splits) {
+    if (batch_size <= 0 || num_heads <= 0 || d_head <= 0 || num_splits <= 0) return 0;
+    const size_t parts = (size_t)batch_size * num_heads * num_splits;
+    return align256(parts * d_head * sizeof(float)) + align256(parts * sizeof(float));
+}
+
+FA_EXPORT int fa_decode_default_splits(int batch_size, int num_heads, int seq_len_kv) {
+    if (batch_size <= 0 || num_heads <= 0 || seq_len_kv <= 0) return 0;
+    DeviceState* st = device_state();
+    const int sms = st ? st->sm_count : 148;
+    const long long bh = (long long)batch_size * num_heads;
+    // Enough CTAs for ~8 per SM, but never fewer than 512 keys per split.
+    long long want = (8ll * sms + bh - 1) / bh;
+    long long max_by_len = seq_len_kv / 512 > 0 ? seq_len_kv / 512 : 1;
+    long long s = want < max_by_len ? want : max_by_len;
+    if (s < 1) s = 1;
+    if (s > FA_MAX_SPLITS) s = FA_MAX_SPLITS;
+    return (int)s;
+}
+
+FA_EXPORT int fa_decode(const fa_decode_args* a) {
+    if (!a || !a->q || !a->k || !a->v) return FA_ERR_INVALID_ARGUMENT;
+    if (!a->o && !a->o_f32) return FA_ERR_INVALID_ARGUMENT;
+    if (a->o_f32 && !a->lse) return FA_ERR_INVALID_ARGUMENT;
+    if (a->batch_size <= 0 || a->num_heads <= 0 || a->seq_len_kv <= 0) return FA_ERR_INVALID_ARGUMENT;
+    if (!(a->scale > 0.0f) || !std::isfinite(a->scale)) return FA_ERR_INVALID_ARGUMENT;
+    if (a->dtype != FA_DTYPE_F16 && a->dtype != FA_DTYPE_BF16) return FA_ERR_UNSUPPORTED;
+    if (a->d_head != 64 && a->d_head != 128) return FA_ERR_UNSUPPORTED;
+    if (a->num_splits < 0 || a->num_splits > FA_MAX_SPLITS) return FA_ERR_UNSUPPORTED;
+    const long long bh = (long long)a->batch_size * a->num_heads;
+    if (bh > 65535) return FA_ERR_UNSUPPORTED;      // grid.y
+    if (!aligned16(a->q) || !aligned16(a->k) || !aligned16(a->v) || (a->o && !aligned16(a->o)))
+        return FA_ERR_MISALIGNED;
+    DeviceState* st = device_state();
+    if (!st) return FA_ERR_CUDA;
+    if (st->cc_major != 10) return FA_ERR_NOT_SM100;
+
+    int splits = a->num_splits ? a->num_splits
+                               : fa_decode_default_splits(a->batch_size, a->num_heads, a->seq_len_kv);
+    if (splits > a->seq_len_kv) splits = a->seq_len_kv;
+    int kps = (a->seq_len_kv + splits - 1) / splits;
+    splits = (a->seq_len_kv + kps - 1) / kps;        // no empty trailing split
+    const size_t need = fa_decode_workspace_bytes(a->batch_size, a->num_heads, a->d_head, splits);
+    if (!a->workspace || a->workspace_bytes < need || !aligned16(a->workspace)) return FA_ERR_WORKSPACE;
+
+    float* o_part = static_cast<float*>(a->workspace);
+    float* lse_part = reinterpret_cast<float*>(static_cast<uint8_t*>(a->workspace) +
+                                               align256((size_t)bh * splits * a->d_head * sizeof(float)));
+    cudaStream_t stream = static_cast<cudaStream_t>(a->stream);
+    const dim3 grid(splits, (unsigned)bh);
+    const float sl2 = a->scale * kLog2e;
+    const uint16_t* q = static_cast<const uint16_t*>(a->q);
+    const uint16_t* k = static_cast<const uint16_t*>(a->k);
+    const uint16_t* v = static_cast<const uint16_t*>(a->v);
+    const bool bf = a->dtype == FA_DTYPE_BF16;
+#define FA_LAUNCH_DECODE(DH, BF) \
+    decode_partial_kernel<DH, BF><<<grid, kDecodeWarps * 32, 0, stream>>>(q, k, v, o_part, lse_part, \
+        a->seq_len_kv, splits, kps, sl2)
+    if (a->d_head == 128) { if (bf) FA_LAUNCH_DECODE(128, true); else FA_LAUNCH_DECODE(128, false); }
+    else                  { if (bf) FA_LAUNCH_DECODE(64, true);  else FA_LAUNCH_DECODE(64, false); }
+#undef FA_LAUNCH_DECODE
+    FA_CUDA_TRY(cudaGetLastError());
+    // partials: o [bh][split][D], lse [bh][split]
+    return launch_combine(o_part, lse_part, splits, a->d_head, (long long)splits * a->d_head, 1, splits,
+                          (int)bh, a->d_head, a->o, a->lse, a->o_f32, a->dtype, stream);
+}
+
+FA_EXPORT int fa_combine(const float* o_parts, const float* lse_parts, int n_parts, int rows,
+                         int d_head, void* o, float* lse, int dtype, void* stream) {
+    if (!o_parts || !lse_parts || !o || n_parts <= 0 || rows <= 0) return FA_ERR_INVALID_ARGUMENT;
+    if (d_head != 64 && d_head != 128) return FA_ERR_UNSUPPORTED;
+    if (dtype != FA_DTYPE_F16 && dtype != FA_DTYPE_BF16) return FA_ERR_UNSUPPORTED;
+    DeviceState* st = device_state();
+    if (!st) return FA_ERR_CUDA;
+    // gathered layout: o [part][row][D], lse [part][row]
+    return launch_combine(o_parts, lse_parts, n_parts, (long long)rows * d_head, d_head, rows, 1, rows,
+                          d_head, o, lse, nullptr, dtype, static_cast<cudaStream_t>(stream));
+}

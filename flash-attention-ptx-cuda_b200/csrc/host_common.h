@@ -1,0 +1,54 @@
+// Host-side plumbing shared by the entry points: per-device state (SM count,
+// status word, staging buffers), the tensor-map encoder and error bookkeeping.
+//
+// The reference caches one SM count for the whole process
+// (kernels/flash_attention.cu:582-591, get_sm_count); here the state is kept
+// per device so that one process can drive several GPUs.
+#pragma once
+
+#include <cstddef>
+#include <cstdint>
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include "../../include/fa_b200.h"
+
+#define FA_EXPORT extern "C" __attribute__((visibility("default")))
+
+namespace fa {
+
+struct DeviceState {
+    int    device      = -1;
+    int    sm_count    = 0;
+    int    cc_major    = 0;
+    int*   status      = nullptr;   // device int, error word written by kernels
+    void*  stage[8]    = {};        // host-entry staging buffers (device memory)
+    size_t stage_bytes[8] = {};
+};
+
+// State of the current device (created on first use).  nullptr on CUDA failure.
+DeviceState* device_state();
+
+// Remembers a CUDA failure for fa_last_cuda_error() and returns FA_ERR_CUDA.
+int note_cuda_error(cudaError_t err, const char* where);
+int note_driver_error(CUresult err, const char* where);
+
+#define FA_CUDA_TRY(expr)                                               \
+    do {                                                                \
+        cudaError_t fa_try_err_ = (expr);                               \
+        if (fa_try_err_ != cudaSuccess) return ::fa::note_cuda_error(fa_try_err_, #expr); \
+    } while (0)
+
+// Rank-3 tiled tensor map over a dense [n_heads, n_rows, row_elems] tensor with
+// 128-byte swizzle.  box_cols * elem_bytes must be 128; box_rows <= 256.
+// dtype is an FA_DTYPE_* value.
+int make_tensor_map_3d(CUtensorMap* out, const void* base, int dtype, uint64_t row_elems,
+                       uint64_t n_rows, uint64_t n_heads, uint32_t box_cols, uint32_t box_rows);
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// Implemented next to their kernels.
+int launch_prefill_16bit(const fa_prefill_args& a, DeviceState* st);
+int launch_prefill_fp8(const fa_prefill_args& a, DeviceState* st);
+
+}  // namespace fa

@@ -1,0 +1,164 @@
+/*
+ * C ABI of the B200 (sm_100a) flash-attention forward library, libfa_b200.so.
+ *
+ * This is the boundary a foreign-function binding attaches to: plain pointers,
+ * sizes and ints, no C++ or framework types.  Every entry point returns FA_OK
+ * (0) or a negative FA_ERR_* code and never terminates the process.
+ *
+ * The C++ interface of the reference project stays available, source
+ * compatible, in include/flash_attention.h (transformer::FlashAttentionParams,
+ * transformer::launch_flash_attention); it is a thin shim over fa_prefill().
+ *
+ * Tensors are dense, row-major, [batch_size * num_heads, seq_len, d_head],
+ * exactly the layout the reference documents (include/flash_attention.h:21-22,
+ * 52-56).  LSE is the natural-log log-sum-exp of the scaled scores, fp32,
+ * [batch_size * num_heads, seq_len] (kernels/flash_attention.cu:498-505).
+ * Causal masking keeps key j for query i iff j <= i
+ * (kernels/flash_attention.cu:307-312, oracle src/demo.cu:41).
+ *
+ * All device pointers must be 16-byte aligned.  Kernels are enqueued on the
+ * given stream and the call returns without synchronising, like the
+ * reference's launch (kernels/flash_attention.cu:567-578).
+ */
+#ifndef FA_B200_H_
+#define FA_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FA_OK                    0
+#define FA_ERR_INVALID_ARGUMENT (-1)  /* null pointer, non-positive size, scale <= 0 or not finite */
+#define FA_ERR_UNSUPPORTED      (-2)  /* d_head / dtype / split count outside what is built */
+#define FA_ERR_MISALIGNED       (-3)  /* a device pointer is not 16-byte aligned */
+#define FA_ERR_WORKSPACE        (-4)  /* workspace missing or too small */
+#define FA_ERR_CUDA             (-5)  /* a CUDA runtime/driver call failed; see fa_last_cuda_error() */
+#define FA_ERR_DEVICE_TIMEOUT   (-6)  /* a kernel gave up on a bounded wait; see fa_device_status() */
+#define FA_ERR_NOT_SM100        (-7)  /* the current device is not compute capability 10.x */
+
+enum { FA_DTYPE_F16 = 0, FA_DTYPE_BF16 = 1, FA_DTYPE_E4M3 = 2 };
+
+/*
+ * Prefill (self-attention forward, Sq == Skv).  Replaces
+ * transformer::launch_flash_attention (include/flash_attention.h:51-67,
+ * kernels/flash_attention.cu:595-617) and the kernel behind it
+ * (kernels/flash_attention.cu:116-507).
+ *
+ * dtype F16 : q,k,v,o fp16.        dtype BF16: q,k,v,o bf16.
+ * dtype E4M3: q,k,v e4m3 codes with per-(batch*head) dequantisation scales
+ *             q_scale,k_scale,v_scale (device, fp32, [batch_size*num_heads],
+ *             value = code * scale); o bf16.
+ * d_head 64 or 128 (E4M3: 128 only).  seq_len any positive value.
+ */
+typedef struct fa_prefill_args {
+    const void*  q;
+    const void*  k;
+    const void*  v;
+    void*        o;
+    float*       lse;          /* optional, may be NULL */
+    int          batch_size;
+    int          num_heads;
+    int          seq_len;
+    int          d_head;
+    float        scale;        /* > 0, typically 1/sqrt(d_head) */
+    int          causal;       /* 0 / 1 */
+    int          dtype;        /* FA_DTYPE_* */
+    const float* q_scale;      /* E4M3 only, else NULL */
+    const float* k_scale;
+    const float* v_scale;
+    void*        stream;       /* cudaStream_t */
+} fa_prefill_args;
+
+int fa_prefill(const fa_prefill_args* args);
+
+/*
+ * Same computation with HOST buffers: copies q,k,v (and the scales) to the
+ * device, runs fa_prefill, copies o (and lse) back and synchronises.  This is
+ * the call pattern of the reference's own verification and demo programs
+ * (src/bench.cu:250-275, src/demo.cu:282-322: cudaMalloc, cudaMemcpy H2D,
+ * launch, cudaMemcpy D2H) folded into one entry point.  Device staging
+ * buffers are kept per device and grown on demand.  `stream` is ignored.
+ */
+int fa_prefill_host(const fa_prefill_args* args_with_host_pointers);
+
+/*
+ * Split-KV decode: one query row per (batch, head) against a KV cache of
+ * seq_len_kv keys, every key visible (no mask).  The reference has no decode
+ * path; the definition is the reference attention (src/demo.cu:28-70) applied
+ * to a single query row.  q, o: [batch_size*num_heads, d_head]; k, v:
+ * [batch_size*num_heads, seq_len_kv, d_head]; fp16 or bf16; d_head 64 or 128.
+ *
+ * The key range is cut into num_splits contiguous slices (0 = choose); each
+ * slice produces a partial (O, LSE) in `workspace`, and a second kernel merges
+ * the partials by their LSEs and writes o (16-bit) and, if given, lse.
+ * If o_f32 is non-NULL the merged, normalised output is ALSO written there in
+ * fp32 ([batch_size*num_heads, d_head]); together with lse this is the partial
+ * result a rank contributes when the KV sequence is sharded across GPUs.
+ */
+typedef struct fa_decode_args {
+    const void* q;
+    const void* k;
+    const void* v;
+    void*       o;             /* may be NULL when o_f32 is given */
+    float*      lse;           /* optional unless o_f32 is given */
+    float*      o_f32;         /* optional */
+    int         batch_size;
+    int         num_heads;
+    int         seq_len_kv;
+    int         d_head;
+    float       scale;
+    int         dtype;         /* FA_DTYPE_F16 or FA_DTYPE_BF16 */
+    int         num_splits;    /* 0 = library chooses; else 1..FA_MAX_SPLITS */
+    void*       workspace;     /* device, >= fa_decode_workspace_bytes(...) */
+    size_t      workspace_bytes;
+    void*       stream;
+} fa_decode_args;
+
+#define FA_MAX_SPLITS 256
+
+size_t fa_decode_workspace_bytes(int batch_size, int num_heads, int d_head, int num_splits);
+int    fa_decode_default_splits(int batch_size, int num_heads, int seq_len_kv);
+int    fa_decode(const fa_decode_args* args);
+
+/*
+ * LSE merge of n_parts partial results (the exchange step of KV-sequence
+ * sharded decode: each rank's (o_f32, lse) gathered into one local buffer).
+ *   o_parts  : fp32 [n_parts, rows, d_head]   lse_parts: fp32 [n_parts, rows]
+ *   o        : 16-bit [rows, d_head] (dtype F16 or BF16)   lse: optional [rows]
+ * m = max_p lse_p; w_p = exp(lse_p - m); o = sum w_p o_p / sum w_p;
+ * lse = m + log(sum w_p).
+ */
+int fa_combine(const float* o_parts, const float* lse_parts, int n_parts, int rows, int d_head,
+               void* o, float* lse, int dtype, void* stream);
+
+/*
+ * Tensor-core known-answer test (the role of test_ptx_mma in the reference,
+ * src/bench.cu:51-165, for the tcgen05 path): one CTA computes
+ *   S = Q K^T            (Q [128,d_head], K [128,d_head], 16-bit, from host)
+ *   P = round16(S * p_scale)
+ *   O = P V              (V [128,d_head])
+ * through the same TMA tensor maps, shared-memory descriptors, TMEM layout and
+ * instruction descriptors the attention kernels use, and returns S [128,128]
+ * and O [128,d_head] in fp32 to host memory.  Synchronous.
+ */
+int fa_kat(int dtype, int d_head, const void* q_host, const void* k_host, const void* v_host,
+           float p_scale, float* s_out_host, float* o_out_host);
+
+/*
+ * Device status word of the current device: 0, or the first error a kernel
+ * recorded since the last clear ((code << 16) | detail; code 1 = a bounded
+ * wait timed out, detail = barrier id).  Synchronises the device.
+ */
+int         fa_device_status(int* status_word);
+int         fa_clear_device_status(void);
+const char* fa_error_string(int code);
+const char* fa_last_cuda_error(void);
+int         fa_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FA_B200_H_ */
