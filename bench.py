@@ -1,0 +1,403 @@
+#!/usr/bin/env python
+"""Benchmark of the attention forward hot path on B200.
+
+``python bench.py --gpus N --steps K --warmup W`` (under torchrun for N > 1)
+prints ONE JSON line on rank 0.
+
+Workload (N = 1): causal prefill, fp16, B=8 H=12 S=2048 D=64, scale 1/8 - the
+shape the reference's headline number is quoted on.  A "step" is one
+``fa_prefill`` launch over that batch.  For N > 1 every rank runs the same
+per-GPU batch on its own GPU (weak scaling over the batch x head axis, no
+collective on the data path); the line also carries the strong-scaling split of
+the same 96 heads for comparison.
+
+``value``     whole-job TFLOP/s with inputs resident in HBM (causal FLOP count
+              4*BH*D*S*(S+1)/2; the reference's own convention 4*BH*S^2*D, which
+              counts masked work, is given as ``tflops_refconv``).
+``e2e``       same metric through ``fa_prefill_host``: pinned host buffers, H2D
+              of Q,K,V and D2H of O and LSE inside the timed region, every step.
+``roofline``  tensor-core roofline of the prefill kernel against the measured
+              cuBLAS bf16 peak; ``decode`` carries the HBM roofline of the
+              split-KV decode kernel (B=32 H=32 Skv=16384 D=128, 16 splits).
+``cpu_baseline``  the reference's own cpu_attention (oracle/_ref) on the host
+              cores, same metric, reported only.
+
+``--impl reference`` times that CPU implementation alone on the same config.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+L2_BYTES = 126 * 1024 * 1024
+CFG = dict(B=8, H=12, S=2048, D=64)
+DEC = dict(B=32, H=32, SKV=16384, D=128, SPLITS=16)
+
+
+def causal_flops(bh, s, d):
+    return 4 * bh * d * s * (s + 1) // 2
+
+
+def refconv_flops(bh, s, d):
+    return 4 * bh * s * s * d
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return dict(hbm_gbs=p["hbm_gbs"], tflops=p["bf16_tflops"],
+                    tflops_sustained=p.get("bf16_tflops_sustained"), source="measured")
+    return dict(hbm_gbs=6650.0, tflops=1590.0, tflops_sustained=1400.0, source="fallback")
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU through NVML (read-only)."""
+
+    def __init__(self, index: int):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self._nv = pynvml
+            self._h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self._nv = None
+
+    def _run(self):
+        nv = self._nv
+        names = {
+            "hw_slowdown": getattr(nv, "nvmlClocksEventReasonHwSlowdown", 0x8),
+            "hw_thermal_slowdown": getattr(nv, "nvmlClocksEventReasonHwThermalSlowdown", 0x40),
+            "sw_thermal_slowdown": getattr(nv, "nvmlClocksEventReasonSwThermalSlowdown", 0x20),
+            "sw_power_cap": getattr(nv, "nvmlClocksEventReasonSwPowerCap", 0x4),
+        }
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM))
+                try:
+                    mask = nv.nvmlDeviceGetCurrentClocksEventReasons(self._h)
+                except Exception:
+                    mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self._h)
+                for n, bit in names.items():
+                    if mask & bit:
+                        self.reasons.add(n)
+            except Exception:
+                pass
+            time.sleep(0.002)
+
+    def start(self):
+        if self._nv is not None:
+            self._stop.clear()
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+
+    def stop(self):
+        if self._thread is not None:
+            self._stop.set()
+            self._thread.join()
+            self._thread = None
+
+    def summary(self):
+        med = float(np.median(self.samples)) if self.samples else None
+        return {"sm_mhz": med, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
+                "samples": len(self.samples)}
+
+
+def physical_index(local_rank: int) -> int:
+    vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+    if vis:
+        ids = [x for x in vis.split(",") if x != ""]
+        try:
+            return int(ids[local_rank])
+        except Exception:
+            return local_rank
+    return local_rank
+
+
+# --------------------------------------------------------------------------- reference arm
+def cpu_reference_run(bh_sample: int, steps: int, warmup: int, threads: int):
+    """Times the reference's cpu_attention (or the oracle port when the reference
+    library was not built) on `bh_sample` heads of the workload per step."""
+    from oracle import oracle
+    s, d = CFG["S"], CFG["D"]
+    q, k, v = (oracle.round_to(x, "f16") for x in oracle.normal_inputs(2002, (bh_sample, s, d)))
+    kind = "reference" if oracle.ref_lib() is not None else "port"
+    fn = (lambda: oracle.ref_attention(q, k, v, 0.125, True, threads=threads)) if kind == "reference" \
+        else (lambda: oracle.attention(q, k, v, 0.125, True, threads=threads))
+    for _ in range(warmup):
+        fn()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        fn()
+    dt = (time.perf_counter() - t0) / max(steps, 1)
+    tflops = causal_flops(bh_sample, s, d) / dt / 1e12
+    return kind, tflops, dt
+
+
+def run_reference_arm(args, rank, world):
+    if rank != 0:
+        return
+    cores = os.cpu_count() or 1
+    bh_sample = min(CFG["B"] * CFG["H"], max(8, cores))
+    steps = max(1, min(args.steps, 3))
+    warmup = min(args.warmup, 1)
+    kind, tflops, dt = cpu_reference_run(bh_sample, steps, warmup, cores)
+    sample = (f"{bh_sample} of {CFG['B'] * CFG['H']} heads of the workload per step "
+              f"(S={CFG['S']}, D={CFG['D']}, causal), {steps} timed steps, {warmup} warm-up")
+    line = {
+        "impl": "reference",
+        "metric": "causal prefill TFLOPS (B8 H12 S2048 D64 fp16)",
+        "value": tflops, "unit": "TFLOP/s (causal FLOP count)",
+        "n_gpus": args.gpus, "steps": steps, "warmup": warmup, "ms_per_step": dt * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic: seeded iid N(0,1) rounded to fp16",
+        "config": {"workload": "causal prefill B8 H12 S2048 D64 (CPU: bounded sample of heads)"},
+        "cpu_baseline": {"value": tflops, "unit": "TFLOP/s (causal FLOP count)", "cores": cores,
+                         "kind": kind, "sample": sample},
+        "e2e": {"value": tflops, "unit": "TFLOP/s (causal FLOP count)", "h2d_bytes_per_step": 0,
+                "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# --------------------------------------------------------------------------- B200 arm
+def run_b200_arm(args, rank, local_rank, world):
+    import torch
+    import torch.distributed as dist
+    import __graft_entry__ as ge
+
+    fa = ge.load_package()
+    fa.lib()                                  # fail loudly if the CUDA library is missing
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device; there is no CPU path")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    peaks = load_peaks()
+    fa.clear_device_status()
+
+    B, H, S, D = CFG["B"], CFG["H"], CFG["S"], CFG["D"]
+    bh = B * H
+    scale = 0.125
+    n_sets = 4                                # rotating input sets: 4 x 101 MB > 126 MB of L2
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(2002 + rank)
+    sets = []
+    for _ in range(n_sets):
+        q, k, v = (torch.randn((bh, S, D), device=dev, dtype=torch.float32, generator=gen).to(torch.float16)
+                   for _ in range(3))
+        o = torch.empty_like(q)
+        lse = torch.empty((bh, S), device=dev, dtype=torch.float32)
+        sets.append((q, k, v, o, lse))
+    stream = torch.cuda.current_stream()
+
+    def step(i, n_heads=bh, head0=0):
+        q, k, v, o, lse = sets[i % n_sets]
+        fa.prefill(q[head0:], k[head0:], v[head0:], o[head0:], lse[head0:], 1, n_heads, S, D, scale, True,
+                   dtype="f16", stream=stream)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps, warmup, sampler=None):
+        for i in range(warmup):
+            fn(i)
+        barrier()
+        if sampler:
+            sampler.start()
+        evs = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
+        evs[0].record(stream)
+        for i in range(steps):
+            fn(i)
+            evs[i + 1].record(stream)
+        barrier()
+        if sampler:
+            sampler.stop()
+        total_ms = evs[0].elapsed_time(evs[-1])
+        per = [evs[i].elapsed_time(evs[i + 1]) for i in range(steps)]
+        t = torch.tensor([total_ms], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item()), per
+
+    sampler = ClockSampler(physical_index(local_rank))
+    warmup = max(args.warmup, 3)
+    total_ms, per = timed(step, args.steps, warmup, sampler)
+    ms_per_step = total_ms / args.steps
+    flops_step = causal_flops(bh, S, D)
+    value = world * flops_step / (ms_per_step * 1e-3) / 1e12
+    kernel_ms = float(np.mean(per))
+    achieved = flops_step / (kernel_ms * 1e-3) / 1e12
+
+    # strong-scaling split of the same 96 heads (reported beside the weak-scaling headline)
+    strong = None
+    if world > 1 and bh % world == 0:
+        nh = bh // world
+        s_ms, _ = timed(lambda i: step(i, nh, rank * nh), args.steps, warmup)
+        strong = {"heads_per_gpu": nh, "ms_per_step": s_ms / args.steps,
+                  "tflops": flops_step / (s_ms / args.steps * 1e-3) / 1e12}
+
+    # ---- end to end: fa_prefill_host from pinned host buffers, copies inside the timed region
+    hq, hk, hv = (torch.randn((bh, S, D), dtype=torch.float32).to(torch.float16).pin_memory() for _ in range(3))
+    ho = torch.empty((bh, S, D), dtype=torch.float16).pin_memory()
+    hl = torch.empty((bh, S), dtype=torch.float32).pin_memory()
+    e2e_steps = 0 if args.no_e2e else max(3, min(args.steps, 20))
+
+    def e2e_step(_i):
+        rc = fa.prefill_raw(hq.data_ptr(), hk.data_ptr(), hv.data_ptr(), ho.data_ptr(), hl.data_ptr(),
+                            1, bh, S, D, scale, True, dtype="f16", host=True)
+        if rc != 0:
+            raise RuntimeError(f"fa_prefill_host failed: {fa.error_string(rc)}")
+
+    for i in range(min(2, e2e_steps)):
+        e2e_step(i)
+    barrier()
+    t0 = time.perf_counter()
+    for i in range(e2e_steps):
+        e2e_step(i)                           # synchronous: returns after the D2H copy completed
+    barrier()
+    e2e_s = (time.perf_counter() - t0) / max(e2e_steps, 1) if e2e_steps else float("inf")
+    te = torch.tensor([e2e_s], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(te, op=dist.ReduceOp.MAX)
+    e2e_s = float(te.item())
+    e2e_val = world * flops_step / e2e_s / 1e12
+    h2d = 3 * bh * S * D * 2
+    d2h = bh * S * D * 2 + bh * S * 4
+    status = fa.device_status()
+
+    # ---- decode HBM roofline (rank-local; reported from rank 0)
+    decode = None
+    if not args.no_decode:
+        decode = run_decode_bench(fa, torch, dev, stream, peaks, args)
+
+    clocks = sampler.summary()
+    cpu_baseline = None
+    if rank == 0 and world == 1 and not args.no_cpu:
+        cores = os.cpu_count() or 1
+        kind, tf, dt = cpu_reference_run(bh, 1, 0, cores)
+        cpu_baseline = {"value": tf, "unit": "TFLOP/s (causal FLOP count)", "cores": cores, "kind": kind,
+                        "sample": f"all {bh} heads of the workload once ({dt:.2f} s wall)"}
+
+    if rank == 0:
+        line = {
+            "metric": "causal prefill TFLOPS (B8 H12 S2048 D64 fp16)",
+            "value": value, "unit": "TFLOP/s (causal FLOP count)",
+            "n_gpus": world, "steps": args.steps, "warmup": warmup, "ms_per_step": ms_per_step,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16",
+            "data": "synthetic: seeded iid N(0,1) rounded to fp16",
+            "config": {"workload": "causal prefill fp16 B=8 H=12 S=2048 D=64 scale=1/8, per GPU",
+                       "global_batch": B * world, "parallelism": f"(batch x head) sharding, dp{world}, no collective",
+                       "l2": f"{n_sets} rotating input sets ({n_sets * 4 * bh * S * D * 2 // 2**20} MiB) > 126 MiB L2"},
+            "tflops_refconv": world * refconv_flops(bh, S, D) / (ms_per_step * 1e-3) / 1e12,
+            "roofline": {"bound": "tensor", "achieved": achieved, "peak": peaks["tflops"], "unit": "TFLOP/s",
+                         "frac": achieved / peaks["tflops"], "traffic": None, "peak_source": peaks["source"],
+                         "kernel": "prefill_kernel<64,128,2,2,causal,f16>", "kernel_ms": kernel_ms},
+            "e2e": {"value": e2e_val, "unit": "TFLOP/s (causal FLOP count)", "h2d_bytes_per_step": h2d,
+                    "d2h_bytes_per_step": d2h, "ms_per_step": e2e_s * 1e3, "steps": e2e_steps},
+            "gpu_launches": args.steps,
+            "clocks": clocks,
+            "device_status": status,
+        }
+        if strong:
+            line["strong_scaling_96_heads"] = strong
+        if decode:
+            line["decode"] = decode
+        if cpu_baseline:
+            line["cpu_baseline"] = cpu_baseline
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def run_decode_bench(fa, torch, dev, stream, peaks, args):
+    B, H, SKV, D, SPLITS = DEC["B"], DEC["H"], DEC["SKV"], DEC["D"], DEC["SPLITS"]
+    bh = B * H
+    k = torch.empty((bh, SKV, D), device=dev, dtype=torch.float16)
+    v = torch.empty((bh, SKV, D), device=dev, dtype=torch.float16)
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(4004)
+    for t in (k, v):                          # fill in slabs to bound temporary memory
+        for i in range(0, bh, 64):
+            t[i:i + 64] = torch.randn((min(64, bh - i), SKV, D), device=dev, dtype=torch.float32,
+                                      generator=gen).to(torch.float16)
+    q = torch.randn((bh, D), device=dev, dtype=torch.float32, generator=gen).to(torch.float16)
+    o = torch.empty((bh, D), device=dev, dtype=torch.float16)
+    lse = torch.empty((bh,), device=dev, dtype=torch.float32)
+    wsb = fa.decode_workspace_bytes(B, H, D, SPLITS)
+    ws = torch.empty(wsb, device=dev, dtype=torch.uint8)
+    scale = float(1.0 / np.sqrt(D))
+
+    def step():
+        fa.decode(q, k, v, o, lse, None, B, H, SKV, D, scale, dtype="f16", num_splits=SPLITS,
+                  workspace=ws, workspace_bytes=wsb, stream=stream)
+
+    steps = max(5, min(args.steps, 30))
+    for _ in range(3):
+        step()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(steps):
+        step()
+    e1.record(stream)
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    algo_bytes = 2 * bh * SKV * D * 2 + 2 * bh * D * 2
+    gbs = algo_bytes / (ms * 1e-3) / 1e9
+    del k, v
+    return {"workload": f"split-KV decode fp16 B={B} H={H} Skv={SKV} D={D}, {SPLITS} splits + combine",
+            "ms_per_step": ms, "tokens_per_s": B / (ms * 1e-3), "steps": steps,
+            "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                         "frac": gbs / peaks["hbm_gbs"], "traffic": None, "peak_source": peaks["source"],
+                         "algorithmic_bytes": algo_bytes,
+                         "note": "K+V (8.59 GB) exceed L2; both kernels (partial + combine) inside the timed step"}}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--no-decode", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--batch", type=int, default=0,
+                    help="profiling only: override the prefill batch (the line is then not the headline)")
+    ap.add_argument("--decode-batch", type=int, default=0,
+                    help="profiling only: override the decode batch")
+    ap.add_argument("--no-cpu", action="store_true")
+    args = ap.parse_args()
+    if args.batch:
+        CFG["B"] = args.batch
+    if args.decode_batch:
+        DEC["B"] = args.decode_batch
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.impl == "reference":
+        run_reference_arm(args, rank, world)
+        return
+    run_b200_arm(args, rank, local_rank, world)
+
+
+if __name__ == "__main__":
+    main()

@@ -53,8 +53,10 @@ def test_bf16(fa, dev, oracle, d, causal):
     o_ref, l_ref = oracle.attention(q, k, v, scale, causal)
     assert np.abs(lse - l_ref).max() < TOL_LSE
     assert np.abs(o - o_ref).max() < TOL_O_BF16
-    ulp = np.maximum(np.abs(o_ref), 2.0 ** -126) * 2.0 ** -7
-    assert (np.abs(o - oracle.round_to(o_ref, "bf16")) <= 2 * ulp + 1e-3).all()
+    # against the oracle rounded to bf16: 2 output ulps plus the effect of P being
+    # rounded to bf16 before P V (relative 2^-9 per weight, |V| up to ~4)
+    ulp = np.abs(o_ref) * 2.0 ** -7
+    assert (np.abs(o - oracle.round_to(o_ref, "bf16")) <= 2 * ulp + 5e-3).all()
 
 
 def test_config1_b1_h12_s512_d64_causal(fa, dev, oracle):
