@@ -10,7 +10,7 @@
 // structure: no mma.sync, no ldmatrix, no cp.async, no block-wide barriers in
 // the loop.
 //
-// One CTA owns one 128-row query tile of one (batch, head):
+// One CTA (8 warps) owns one 128-row query tile of one (batch, head):
 //   warp 4 (one lane)  TMA producer: Q once, then K and V tiles through two
 //                      mbarrier-guarded shared-memory rings (128-byte swizzle);
 //   warp 5 (one lane)  issues tcgen05.mma: S = Q K^T into TMEM, later
@@ -30,32 +30,46 @@
 
 #include "host_common.h"
 #include "ptx.cuh"
+#include "tmem_ld.cuh"
 
 namespace fa {
 namespace {
 
 constexpr int kBM = 128;                 // query rows per CTA
-constexpr int kThreads = 192;            // 4 softmax warps + TMA warp + MMA warp
+constexpr int kThreads = 256;            // warps 0-3 softmax, 4 TMA, 5 MMA, 6-7 only donate registers
+constexpr int kRegsSoftmax = 208;        // setmaxnreg targets: 128 * (208 + 48) = 256 * 128
+constexpr int kRegsOther = 48;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 constexpr float kRescaleThreshold = 8.0f;   // log2 units: rescale only if max grew > 2^8
 
 // Barrier ids reported in the status word when a wait gives up.
 enum : int { kBarQ = 1, kBarKFull = 2, kBarKEmpty = 3, kBarVFull = 4, kBarVEmpty = 5,
-             kBarSFull = 6, kBarPFull = 7, kBarOFull = 8 };
+             kBarSFull = 6, kBarPFull = 7, kBarOFull = 8, kBarSFree = 9 };
 
-__device__ __forceinline__ void tmem_wait_ld_tie(uint32_t (&r)[32]) {
-    // Waits for outstanding tcgen05.ld and ties the destination registers to the
-    // wait so that no use of them can be scheduled ahead of it.
-    asm volatile("tcgen05.wait::ld.sync.aligned;"
-                 : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]),
-                   "+r"(r[6]), "+r"(r[7]), "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]),
-                   "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]), "+r"(r[16]), "+r"(r[17]),
-                   "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]),
-                   "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]),
-                   "+r"(r[30]), "+r"(r[31])
-                 :
-                 : "memory");
+// Packed pairs of fp32 (sm_100 has two-wide fp32 FMA/ADD on 64-bit register pairs).
+__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float& lo, float& hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
 }
 
 template <int D, int BN, int NK, int NV>
@@ -74,17 +88,20 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o,
                float* __restrict__ lse_out, int seq_len, int n_bh, int n_qtiles, float scale_log2,
                int* status) {
+    static_assert(BN == 128, "the softmax warps hold one full 128-column score row in registers");
     using L = PrefillSmem<D, BN, NK, NV>;
     constexpr int NBOX = L::kNBox;
-    constexpr int NCH  = BN / 32;                         // 32-column chunks of an S row
     constexpr uint32_t S_COL = 0;
     constexpr uint32_t O_COL = 128;
-    constexpr uint32_t P_COL = (D == 64) ? 192 : 0;       // D = 128: P reuses the S columns it replaces
+    // D = 64: P has its own columns, so S is free as soon as the softmax warps hold it in
+    // registers and the next Q K^T can be issued before P V.  D = 128: P reuses the S columns.
+    constexpr bool EARLY_QK = (D == 64);
+    constexpr uint32_t P_COL = EARLY_QK ? 192 : 0;
     constexpr uint32_t TMEM_COLS = 256;
     constexpr uint32_t FMT = BF16 ? kFmtBF16 : kFmtF16;
 
     extern __shared__ uint8_t smem_raw[];
-    __shared__ __align__(8) uint64_t bar_q, bar_s, bar_p, bar_o;
+    __shared__ __align__(8) uint64_t bar_q, bar_s, bar_p, bar_o, bar_sfree;
     __shared__ __align__(8) uint64_t bar_kf[NK], bar_ke[NK], bar_vf[NV], bar_ve[NV];
     __shared__ uint32_t tmem_slot;
     __shared__ int abort_flag;
@@ -107,7 +124,8 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     if (tid == 0) {
         mbar_init(smem_u32(&bar_q), 1);
         mbar_init(smem_u32(&bar_s), 1);
-        mbar_init(smem_u32(&bar_p), 128);
+        mbar_init(smem_u32(&bar_p), 4);          // one arrival per softmax warp
+        mbar_init(smem_u32(&bar_sfree), 4);
         mbar_init(smem_u32(&bar_o), 1);
         for (int i = 0; i < NK; i++) { mbar_init(smem_u32(&bar_kf[i]), 1); mbar_init(smem_u32(&bar_ke[i]), 1); }
         for (int i = 0; i < NV; i++) { mbar_init(smem_u32(&bar_vf[i]), 1); mbar_init(smem_u32(&bar_ve[i]), 1); }
@@ -125,9 +143,10 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     tc_fence_after();
     const uint32_t tmem = tmem_slot;
 
-    if (warp == 4) {
-        // ------------------------------------------------------------ TMA producer
-        if (lane == 0) {
+    if (warp >= 4) {
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsOther));
+        if (warp == 4 && lane == 0) {
+            // -------------------------------------------------------- TMA producer
             mbar_arrive_expect_tx(smem_u32(&bar_q), L::kQBytes);
             for (int b = 0; b < NBOX; b++)
                 tma_load_3d(q_s + b * L::kQBoxBytes, &tm_q, smem_u32(&bar_q), b * 64, q_start, bh);
@@ -144,19 +163,17 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                     tma_load_3d(v_s + sv * L::kKVBytes + b * L::kKVBoxBytes, &tm_v,
                                 smem_u32(&bar_vf[sv]), b * 64, j * BN, bh);
             }
-        }
-        __syncwarp();
-    } else if (warp == 5) {
-        // ------------------------------------------------------------ MMA issuer
-        if (lane == 0) {
+        } else if (warp == 5 && lane == 0) {
+            // -------------------------------------------------------- MMA issuer
             constexpr uint32_t idesc_qk = make_idesc(kBM, BN, FMT, FMT, kMajorK, kMajorK);
             constexpr uint32_t idesc_pv = make_idesc(kBM, D, FMT, FMT, kMajorK, kMajorMN);
             constexpr uint64_t hi_k = make_sdesc_hi(16, 1024);
             constexpr uint64_t hi_v = make_sdesc_hi(L::kKVBoxBytes, 1024);
-            bool ok = mbar_wait(smem_u32(&bar_q), 0, ctl, kBarQ);
-            for (int j = 0; ok && j < n_kv; j++) {
-                const int sk = j % NK, sv = j % NV;
-                if (!mbar_wait(smem_u32(&bar_kf[sk]), (j / NK) & 1, ctl, kBarKFull)) break;
+            auto issue_qk = [&](int j) -> bool {
+                const int sk = j % NK;
+                if (!mbar_wait(smem_u32(&bar_kf[sk]), (j / NK) & 1, ctl, kBarKFull)) return false;
+                if (EARLY_QK && j > 0 &&
+                    !mbar_wait(smem_u32(&bar_sfree), (j - 1) & 1, ctl, kBarSFree)) return false;
                 tc_fence_after();
                 const uint32_t kb = k_s + sk * L::kKVBytes;
 #pragma unroll
@@ -168,8 +185,12 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                 }
                 tc_commit(smem_u32(&bar_s));
                 tc_commit(smem_u32(&bar_ke[sk]));
-                if (!mbar_wait(smem_u32(&bar_vf[sv]), (j / NV) & 1, ctl, kBarVFull)) break;
-                if (!mbar_wait(smem_u32(&bar_p), j & 1, ctl, kBarPFull)) break;
+                return true;
+            };
+            auto issue_pv = [&](int j) -> bool {
+                const int sv = j % NV;
+                if (!mbar_wait(smem_u32(&bar_vf[sv]), (j / NV) & 1, ctl, kBarVFull)) return false;
+                if (!mbar_wait(smem_u32(&bar_p), j & 1, ctl, kBarPFull)) return false;
                 tc_fence_after();
                 const uint32_t vb = v_s + sv * L::kKVBytes;
 #pragma unroll
@@ -178,10 +199,23 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                                idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
                 tc_commit(smem_u32(&bar_o));
                 tc_commit(smem_u32(&bar_ve[sv]));
+                return true;
+            };
+            bool ok = mbar_wait(smem_u32(&bar_q), 0, ctl, kBarQ);
+            if (EARLY_QK) {
+                // S(j+1) is computed while the softmax warps still work on S(j).
+                ok = ok && issue_qk(0);
+                for (int j = 0; ok && j < n_kv; j++) {
+                    if (j + 1 < n_kv) ok = issue_qk(j + 1);
+                    ok = ok && issue_pv(j);
+                }
+            } else {
+                for (int j = 0; ok && j < n_kv; j++) ok = issue_qk(j) && issue_pv(j);
             }
         }
         __syncwarp();
     } else {
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegsSoftmax));
         // ------------------------------------------------------------ softmax + epilogue
         const int r_in_tile = tid;                       // 0..127 == TMEM lane
         const int row = q_start + r_in_tile;
@@ -191,111 +225,110 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         const uint32_t t_o = tmem + lane_off + O_COL;
         const int row_limit = CAUSAL ? min(seq_len, row + 1) : seq_len;   // keys [0,row_limit) visible
         const int tile_min_limit = CAUSAL ? min(seq_len, q_start + 1) : seq_len;
-        float m_used = 0.0f, l_run = 0.0f;
+        const uint64_t scale2 = pack2(scale_log2, scale_log2);
+        float m_used = 0.0f;
+        uint64_t lsum2 = pack2(0.0f, 0.0f);              // running row sum, two partial lanes
         bool ok = true;
 
         for (int j = 0; j < n_kv; j++) {
             const int kv_start = j * BN;
-            // The vote keeps the warp together: every lane leaves the loop or none does.
+            // The votes keep the warp together: every lane leaves the loop or none does.
             if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&bar_s), j & 1, ctl, kBarSFull))) { ok = false; break; }
             tc_fence_after();
-            const bool masked_tile = (tile_min_limit - kv_start) < BN;
-            const int limit = row_limit - kv_start;       // columns [0,limit) of this tile are visible
-
-            uint32_t ra[32], rb[32];
-            // ---- pass 1: row maximum of the raw scores
-            float mx = -INFINITY;
-            tmem_ld_x32(t_s, ra);
-#pragma unroll
-            for (int c = 0; c < NCH; c++) {
-                uint32_t (&cur)[32] = (c & 1) ? rb : ra;
-                uint32_t (&nxt)[32] = (c & 1) ? ra : rb;
-                tmem_wait_ld_tie(cur);
-                if (c + 1 < NCH) tmem_ld_x32(t_s + (c + 1) * 32, nxt);
-                if (masked_tile) {
-#pragma unroll
-                    for (int i = 0; i < 32; i++)
-                        mx = fmaxf(mx, (c * 32 + i < limit) ? __uint_as_float(cur[i]) : -INFINITY);
-                } else {
-#pragma unroll
-                    for (int i = 0; i < 32; i++) mx = fmaxf(mx, __uint_as_float(cur[i]));
-                }
+            uint32_t s[128];
+            tmem_ld128_wait(t_s, s);
+            if (EARLY_QK) {                              // S is in registers: release the TMEM columns
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&bar_sfree));
             }
-            const float tile_max = mx * scale_log2;
+            if ((tile_min_limit - kv_start) < BN) {      // tile touches the mask or the ragged end
+                const int limit = row_limit - kv_start;  // columns [0,limit) are visible
+#pragma unroll
+                for (int i = 0; i < 128; i++) s[i] = (i < limit) ? s[i] : 0xff800000u;   // -inf
+            }
+            // ---- row maximum of the raw scores
+            float a0 = -INFINITY, a1 = -INFINITY, a2 = -INFINITY, a3 = -INFINITY;
+#pragma unroll
+            for (int i = 0; i < 128; i += 8) {
+                a0 = max3(a0, __uint_as_float(s[i]), __uint_as_float(s[i + 1]));
+                a1 = max3(a1, __uint_as_float(s[i + 2]), __uint_as_float(s[i + 3]));
+                a2 = max3(a2, __uint_as_float(s[i + 4]), __uint_as_float(s[i + 5]));
+                a3 = max3(a3, __uint_as_float(s[i + 6]), __uint_as_float(s[i + 7]));
+            }
+            const float tile_max = fmaxf(max3(a0, a1, a2), a3) * scale_log2;
             bool need = false;
             if (j == 0) m_used = tile_max;
             else need = tile_max > m_used + kRescaleThreshold;
 
-            // ---- rare: the running max grew by more than the threshold -> rescale O in TMEM
-            if (__any_sync(0xffffffffu, need)) {
+            if (EARLY_QK && j > 0) {
+                // P(j-1) must have been consumed (and O(j-1) accumulated) before P / O are touched.
                 if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&bar_o), (j - 1) & 1, ctl, kBarOFull))) { ok = false; break; }
                 tc_fence_after();
+            }
+            // ---- rare: the running max grew by more than the threshold -> rescale O in TMEM.
+            // (D = 128: S(j) complete implies P V(j-1) complete, the tensor pipe runs in order.)
+            if (__any_sync(0xffffffffu, need)) {
                 float factor = 1.0f;
                 if (need) {
                     factor = ex2_approx(m_used - tile_max);
                     m_used = tile_max;
-                    l_run *= factor;
+                    lsum2 = fma2(lsum2, pack2(factor, factor), pack2(0.0f, 0.0f));
                 }
 #pragma unroll 1
                 for (int c = 0; c < D / 32; c++) {
-                    tmem_ld_x32(t_o + c * 32, ra);
-                    tmem_wait_ld_tie(ra);
+                    uint32_t t[32];
+                    tmem_ld32_wait(t_o + c * 32, t);
 #pragma unroll
-                    for (int i = 0; i < 32; i++) ra[i] = __float_as_uint(__uint_as_float(ra[i]) * factor);
-                    tmem_st_x32(t_o + c * 32, ra);
+                    for (int i = 0; i < 32; i++) t[i] = __float_as_uint(__uint_as_float(t[i]) * factor);
+                    tmem_st_x32(t_o + c * 32, t);
                 }
                 tmem_wait_st();
             }
 
-            // ---- pass 2: p = 2^(s*scale*log2e - m); row sum; P -> TMEM as packed 16-bit
-            const float neg_m = -m_used;
-            float psum = 0.0f;
-            tmem_ld_x32(t_s, ra);
+            // ---- p = 2^(s*scale*log2e - m); row sum; P -> TMEM as packed 16-bit pairs
+            const uint64_t negm2 = pack2(-m_used, -m_used);
 #pragma unroll
-            for (int c = 0; c < NCH; c++) {
-                uint32_t (&cur)[32] = (c & 1) ? rb : ra;
-                uint32_t (&nxt)[32] = (c & 1) ? ra : rb;
-                tmem_wait_ld_tie(cur);
-                if (c + 1 < NCH) tmem_ld_x32(t_s + (c + 1) * 32, nxt);
+            for (int c = 0; c < 4; c++) {
                 uint32_t pk[16];
 #pragma unroll
-                for (int i = 0; i < 32; i += 2) {
-                    float s0 = __uint_as_float(cur[i]), s1 = __uint_as_float(cur[i + 1]);
-                    if (masked_tile) {
-                        s0 = (c * 32 + i < limit) ? s0 : -INFINITY;
-                        s1 = (c * 32 + i + 1 < limit) ? s1 : -INFINITY;
-                    }
-                    const float p0 = ex2_approx(fmaf(s0, scale_log2, neg_m));
-                    const float p1 = ex2_approx(fmaf(s1, scale_log2, neg_m));
-                    psum += p0 + p1;
-                    pk[i >> 1] = pack_16<BF16>(p0, p1);
+                for (int i = 0; i < 16; i++) {
+                    const int e = c * 32 + 2 * i;
+                    const uint64_t t = fma2(pack2(__uint_as_float(s[e]), __uint_as_float(s[e + 1])), scale2, negm2);
+                    float t0, t1;
+                    unpack2(t, t0, t1);
+                    const float p0 = ex2_approx(t0), p1 = ex2_approx(t1);
+                    lsum2 = add2(lsum2, pack2(p0, p1));
+                    pk[i] = pack_16<BF16>(p0, p1);
                 }
                 tmem_st_x16(t_p + c * 16, pk);
             }
-            l_run += psum;
             tmem_wait_st();
             tc_fence_before();
-            mbar_arrive(smem_u32(&bar_p));
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&bar_p));
         }
 
         // ---- epilogue: O / l -> 16-bit -> swizzled staging (the Q buffer) -> TMA store
         ok = __all_sync(0xffffffffu, ok && mbar_wait(smem_u32(&bar_o), (n_kv - 1) & 1, ctl, kBarOFull));
         tc_fence_after();
         if (ok) {
+            float l0, l1;
+            unpack2(lsum2, l0, l1);
+            const float l_run = l0 + l1;
             const float inv_l = 1.0f / l_run;
-            uint32_t ra[32];
 #pragma unroll 1
             for (int c = 0; c < D / 32; c++) {
-                tmem_ld_x32(t_o + c * 32, ra);
-                tmem_wait_ld_tie(ra);
+                uint32_t t[32];
+                tmem_ld32_wait(t_o + c * 32, t);
 #pragma unroll
-                for (int t = 0; t < 4; t++) {
+                for (int g4 = 0; g4 < 4; g4++) {
                     uint32_t w[4];
 #pragma unroll
                     for (int e = 0; e < 4; e++)
-                        w[e] = pack_16<BF16>(__uint_as_float(ra[t * 8 + 2 * e]) * inv_l,
-                                             __uint_as_float(ra[t * 8 + 2 * e + 1]) * inv_l);
-                    const int g = c * 4 + t;              // 8-element (16-byte) group index in the row
+                        w[e] = pack_16<BF16>(__uint_as_float(t[g4 * 8 + 2 * e]) * inv_l,
+                                             __uint_as_float(t[g4 * 8 + 2 * e + 1]) * inv_l);
+                    const int g = c * 4 + g4;             // 8-element (16-byte) group index in the row
                     const uint32_t addr = q_s + (g >> 3) * L::kQBoxBytes + r_in_tile * 128 +
                                           (((g & 7) ^ (r_in_tile & 7)) << 4);
                     asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w[0]),
