@@ -19,7 +19,8 @@ import ctypes
 import os
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(HERE, "libfa_b200.so")
+# FA_B200_LIB points the binding at another build of the same library (development only).
+LIB_PATH = os.environ.get("FA_B200_LIB") or os.path.join(HERE, "libfa_b200.so")
 
 FA_OK = 0
 FA_ERR_INVALID_ARGUMENT = -1

@@ -72,6 +72,17 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
     return d;
 }
 
+#ifdef FA_PHASE_TIMING
+// Development aid (not compiled into the shipped library): per-tile clock stamps of one CTA.
+__device__ long long g_phase_ts[2][64][8];
+__device__ long long g_cta_ts[4096][8];
+#define FA_CTS(k) do { if (blockIdx.x < 4096) { g_cta_ts[blockIdx.x][k] = clock64(); } } while (0)
+#define FA_TS(who, j, k) do { if (blockIdx.x == FA_PHASE_TIMING && (j) < 64) g_phase_ts[who][j][k] = clock64(); } while (0)
+#else
+#define FA_TS(who, j, k) do {} while (0)
+#define FA_CTS(k) do {} while (0)
+#endif
+
 template <int D, int BN, int NK, int NV>
 struct PrefillSmem {
     static constexpr int kNBox      = D / 64;              // 64-column (128-byte) boxes per row
@@ -121,6 +132,14 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     const int kv_len = CAUSAL ? min(seq_len, q_start + kBM) : seq_len;
     const int n_kv = (kv_len + BN - 1) / BN;
 
+#ifdef FA_PHASE_TIMING
+    if (tid == 0 && blockIdx.x < 4096) {
+        unsigned smid; asm volatile("mov.u32 %0, %smid;" : "=r"(smid));
+        g_cta_ts[blockIdx.x][6] = smid;
+        g_cta_ts[blockIdx.x][7] = (long long)global_timer_ns();
+    }
+#endif
+    if (tid == 0) FA_CTS(0);
     if (tid == 0) {
         mbar_init(smem_u32(&bar_q), 1);
         mbar_init(smem_u32(&bar_s), 1);
@@ -142,6 +161,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = tmem_slot;
+    if (tid == 0) FA_CTS(1);
 
     if (warp >= 4) {
         asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsOther));
@@ -175,6 +195,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                 if (EARLY_QK && j > 0 &&
                     !mbar_wait(smem_u32(&bar_sfree), (j - 1) & 1, ctl, kBarSFree)) return false;
                 tc_fence_after();
+                FA_TS(1, j, 0);
                 const uint32_t kb = k_s + sk * L::kKVBytes;
 #pragma unroll
                 for (int kk = 0; kk < D / 16; kk++) {
@@ -185,6 +206,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                 }
                 tc_commit(smem_u32(&bar_s));
                 tc_commit(smem_u32(&bar_ke[sk]));
+                FA_TS(1, j, 1);
                 return true;
             };
             auto issue_pv = [&](int j) -> bool {
@@ -192,6 +214,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                 if (!mbar_wait(smem_u32(&bar_vf[sv]), (j / NV) & 1, ctl, kBarVFull)) return false;
                 if (!mbar_wait(smem_u32(&bar_p), j & 1, ctl, kBarPFull)) return false;
                 tc_fence_after();
+                FA_TS(1, j, 2);
                 const uint32_t vb = v_s + sv * L::kKVBytes;
 #pragma unroll
                 for (int kk = 0; kk < BN / 16; kk++)
@@ -199,6 +222,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                                idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
                 tc_commit(smem_u32(&bar_o));
                 tc_commit(smem_u32(&bar_ve[sv]));
+                FA_TS(1, j, 3);
                 return true;
             };
             bool ok = mbar_wait(smem_u32(&bar_q), 0, ctl, kBarQ);
@@ -235,8 +259,11 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             // The votes keep the warp together: every lane leaves the loop or none does.
             if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&bar_s), j & 1, ctl, kBarSFull))) { ok = false; break; }
             tc_fence_after();
+            if (tid == 0) FA_TS(0, j, 0);
+            if (tid == 0 && j == 0) FA_CTS(2);
             uint32_t s[128];
             tmem_ld128_wait(t_s, s);
+            if (tid == 0) FA_TS(0, j, 1);
             if (EARLY_QK) {                              // S is in registers: release the TMEM columns
                 tc_fence_before();
                 __syncwarp();
@@ -257,18 +284,22 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                 a3 = max3(a3, __uint_as_float(s[i + 6]), __uint_as_float(s[i + 7]));
             }
             const float tile_max = fmaxf(max3(a0, a1, a2), a3) * scale_log2;
+            if (tid == 0) FA_TS(0, j, 2);
             bool need = false;
             if (j == 0) m_used = tile_max;
             else need = tile_max > m_used + kRescaleThreshold;
 
-            if (EARLY_QK && j > 0) {
-                // P(j-1) must have been consumed (and O(j-1) accumulated) before P / O are touched.
-                if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&bar_o), (j - 1) & 1, ctl, kBarOFull))) { ok = false; break; }
-                tc_fence_after();
-            }
             // ---- rare: the running max grew by more than the threshold -> rescale O in TMEM.
-            // (D = 128: S(j) complete implies P V(j-1) complete, the tensor pipe runs in order.)
+            // O(j-1) must be complete first.  D = 128: S(j) complete implies P V(j-1) complete
+            // (the tensor pipe runs in order); D = 64: Q K^T(j) was issued ahead of P V(j-1),
+            // so wait for its commit.
+            bool pv_prev_done = !(EARLY_QK && j > 0);
             if (__any_sync(0xffffffffu, need)) {
+                if (!pv_prev_done) {
+                    if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&bar_o), (j - 1) & 1, ctl, kBarOFull))) { ok = false; break; }
+                    tc_fence_after();
+                    pv_prev_done = true;
+                }
                 float factor = 1.0f;
                 if (need) {
                     factor = ex2_approx(m_used - tile_max);
@@ -286,29 +317,40 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                 tmem_wait_st();
             }
 
-            // ---- p = 2^(s*scale*log2e - m); row sum; P -> TMEM as packed 16-bit pairs
+            if (tid == 0) FA_TS(0, j, 3);
+            // ---- p = 2^(s*scale*log2e - m); row sum; P as packed 16-bit pairs, kept in
+            // registers (they replace the scores two for one) until the P columns are free.
             const uint64_t negm2 = pack2(-m_used, -m_used);
+            uint32_t pk[64];
+#pragma unroll
+            for (int i = 0; i < 64; i++) {
+                const uint64_t t = fma2(pack2(__uint_as_float(s[2 * i]), __uint_as_float(s[2 * i + 1])), scale2, negm2);
+                float t0, t1;
+                unpack2(t, t0, t1);
+                const float p0 = ex2_approx(t0), p1 = ex2_approx(t1);
+                lsum2 = add2(lsum2, pack2(p0, p1));
+                pk[i] = pack_16<BF16>(p0, p1);
+            }
+            if (!pv_prev_done) {
+                // P(j-1) must have been consumed by P V(j-1) before it is overwritten; by now it
+                // normally has been, so this wait rarely blocks.
+                if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&bar_o), (j - 1) & 1, ctl, kBarOFull))) { ok = false; break; }
+                tc_fence_after();
+            }
 #pragma unroll
             for (int c = 0; c < 4; c++) {
-                uint32_t pk[16];
-#pragma unroll
-                for (int i = 0; i < 16; i++) {
-                    const int e = c * 32 + 2 * i;
-                    const uint64_t t = fma2(pack2(__uint_as_float(s[e]), __uint_as_float(s[e + 1])), scale2, negm2);
-                    float t0, t1;
-                    unpack2(t, t0, t1);
-                    const float p0 = ex2_approx(t0), p1 = ex2_approx(t1);
-                    lsum2 = add2(lsum2, pack2(p0, p1));
-                    pk[i] = pack_16<BF16>(p0, p1);
-                }
-                tmem_st_x16(t_p + c * 16, pk);
+                uint32_t (&chunk)[16] = *reinterpret_cast<uint32_t (*)[16]>(&pk[c * 16]);
+                tmem_st_x16(t_p + c * 16, chunk);
             }
+            if (tid == 0) FA_TS(0, j, 4);
             tmem_wait_st();
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&bar_p));
+            if (tid == 0) FA_TS(0, j, 5);
         }
 
+        if (tid == 0) FA_CTS(3);
         // ---- epilogue: O / l -> 16-bit -> swizzled staging (the Q buffer) -> TMA store
         ok = __all_sync(0xffffffffu, ok && mbar_wait(smem_u32(&bar_o), (n_kv - 1) & 1, ctl, kBarOFull));
         tc_fence_after();
@@ -345,8 +387,9 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             for (int b = 0; b < NBOX; b++)
                 tma_store_3d(&tm_o, q_s + b * L::kQBoxBytes, b * 64, q_start, bh);
             tma_store_commit();
-            tma_store_wait_all();
+            tma_store_wait_read();        // the CTA may exit once the staging buffer has been read
         }
+        if (tid == 0) FA_CTS(4);
     }
 
     tc_fence_before();
@@ -396,6 +439,15 @@ int launch_prefill_16bit(const fa_prefill_args& a, DeviceState* st) {
     return FA_DISPATCH(128, 1, 1);
 #undef FA_DISPATCH
 }
+
+#ifdef FA_PHASE_TIMING
+extern "C" __attribute__((visibility("default"))) int fa_debug_phase_ts(long long* out) {
+    return (int)cudaMemcpyFromSymbol(out, g_phase_ts, sizeof(long long) * 2 * 64 * 8);
+}
+extern "C" __attribute__((visibility("default"))) int fa_debug_cta_ts(long long* out) {
+    return (int)cudaMemcpyFromSymbol(out, g_cta_ts, sizeof(long long) * 4096 * 8);
+}
+#endif
 
 // Placeholder until the e4m3 kernel lands: reports the variant as not built.
 int launch_prefill_fp8(const fa_prefill_args&, DeviceState*) { return FA_ERR_UNSUPPORTED; }
