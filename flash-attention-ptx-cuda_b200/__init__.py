@@ -35,7 +35,7 @@ DTYPES = {"f16": FA_DTYPE_F16, "bf16": FA_DTYPE_BF16, "e4m3": FA_DTYPE_E4M3}
 
 # Every symbol include/fa_b200.h declares; the CPU-only tests check they all resolve.
 EXPORTED_SYMBOLS = (
-    "fa_prefill", "fa_prefill_host", "fa_decode", "fa_decode_workspace_bytes",
+    "fa_prefill", "fa_prefill_host", "fa_decode", "fa_decode_static", "fa_decode_workspace_bytes",
     "fa_decode_default_splits", "fa_combine", "fa_kat", "fa_device_status",
     "fa_clear_device_status", "fa_error_string", "fa_last_cuda_error", "fa_version",
 )
@@ -91,6 +91,8 @@ def lib() -> ctypes.CDLL:
         l.fa_prefill_host.argtypes = [ctypes.POINTER(PrefillArgs)]
         l.fa_decode.restype = ctypes.c_int
         l.fa_decode.argtypes = [ctypes.POINTER(DecodeArgs)]
+        l.fa_decode_static.restype = ctypes.c_int
+        l.fa_decode_static.argtypes = [ctypes.POINTER(DecodeArgs)]
         l.fa_decode_workspace_bytes.restype = ctypes.c_size_t
         l.fa_decode_workspace_bytes.argtypes = [ctypes.c_int] * 4
         l.fa_decode_default_splits.restype = ctypes.c_int
@@ -169,6 +171,19 @@ def decode_raw(q, k, v, o, lse, o_f32, batch_size, num_heads, seq_len_kv, d_head
                    seq_len_kv, d_head, scale, DTYPES[dtype] if isinstance(dtype, str) else dtype,
                    num_splits, _ptr(workspace), workspace_bytes, _stream_handle(stream))
     return lib().fa_decode(ctypes.byref(a))
+
+
+DECODE_STATIC_SCRATCH_BYTES = 8 * 1024 * 1024 + 512 * 1024
+
+
+def decode_static_raw(q, k, v, o, lse, o_f32, batch_size, num_heads, seq_len_kv, d_head, scale,
+                      dtype="f16", num_splits=0, stream=None) -> int:
+    """fa_decode_static: decode with the library's built-in scratch array instead of a
+    caller workspace (for callers that may not allocate).  Returns the status code."""
+    a = DecodeArgs(_ptr(q), _ptr(k), _ptr(v), _ptr(o), _ptr(lse), _ptr(o_f32), batch_size, num_heads,
+                   seq_len_kv, d_head, scale, DTYPES[dtype] if isinstance(dtype, str) else dtype,
+                   num_splits, None, 0, _stream_handle(stream))
+    return lib().fa_decode_static(ctypes.byref(a))
 
 
 def decode(*args, **kw) -> None:

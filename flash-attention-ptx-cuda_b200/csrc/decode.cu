@@ -23,6 +23,7 @@
 #include <cmath>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
+#include <mutex>
 
 #include "host_common.h"
 
@@ -299,6 +300,107 @@ FA_EXPORT int fa_decode(const fa_decode_args* a) {
 #undef FA_LAUNCH_DECODE
     FA_CUDA_TRY(cudaGetLastError());
     // partials: o [bh][split][D], lse [bh][split]
+    return launch_combine(o_part, lse_part, splits, a->d_head, (long long)splits * a->d_head, 1, splits,
+                          (int)bh, a->d_head, a->o, a->lse, a->o_f32, a->dtype, stream);
+}
+
+// ---------------------------------------------------------------------------
+// fa_decode_static: split-KV decode for callers that may not allocate.
+//
+// The partial (O, LSE) results go to the file-scope device array below instead
+// of a caller-provided workspace.  In host code the array's name is only a
+// handle, not a device address, so the address is looked up once per device
+// with cudaGetSymbolAddress (with that device current) and that pointer is what
+// the kernels receive.  Nothing on this path allocates: it does not touch the
+// per-device state used by the other entry points (that state owns a
+// cudaMalloc'ed status word), it queries the device attributes directly.
+// ---------------------------------------------------------------------------
+namespace fa {
+namespace {
+
+static __device__ __align__(256) unsigned char g_decode_static_scratch[FA_DECODE_STATIC_SCRATCH_BYTES];
+
+struct StaticScratchSetup {
+    bool  ready = false;
+    void* ptr = nullptr;      // device address of g_decode_static_scratch on this device
+    int   cc_major = 0;
+    int   sm_count = 0;
+};
+StaticScratchSetup g_static_setup[64];
+std::mutex g_static_mutex;
+
+// First call on a device: resolve the array's device address.  Returns FA_OK or an error code.
+int static_scratch_setup(StaticScratchSetup** out) {
+    int dev = 0;
+    FA_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return FA_ERR_INVALID_ARGUMENT;
+    StaticScratchSetup* s = &g_static_setup[dev];
+    if (!s->ready) {
+        std::lock_guard<std::mutex> lock(g_static_mutex);
+        if (!s->ready) {
+            void* ptr = nullptr;
+            FA_CUDA_TRY(cudaGetSymbolAddress(&ptr, g_decode_static_scratch));
+            FA_CUDA_TRY(cudaDeviceGetAttribute(&s->cc_major, cudaDevAttrComputeCapabilityMajor, dev));
+            FA_CUDA_TRY(cudaDeviceGetAttribute(&s->sm_count, cudaDevAttrMultiProcessorCount, dev));
+            s->ptr = ptr;
+            s->ready = true;
+        }
+    }
+    *out = s;
+    return FA_OK;
+}
+
+}  // namespace
+}  // namespace fa
+
+FA_EXPORT int fa_decode_static(const fa_decode_args* a) {
+    if (!a || !a->q || !a->k || !a->v) return FA_ERR_INVALID_ARGUMENT;
+    if (!a->o && !a->o_f32) return FA_ERR_INVALID_ARGUMENT;
+    if (a->o_f32 && !a->lse) return FA_ERR_INVALID_ARGUMENT;
+    if (a->batch_size <= 0 || a->num_heads <= 0 || a->seq_len_kv <= 0) return FA_ERR_INVALID_ARGUMENT;
+    if (!(a->scale > 0.0f) || !std::isfinite(a->scale)) return FA_ERR_INVALID_ARGUMENT;
+    if (a->dtype != FA_DTYPE_F16 && a->dtype != FA_DTYPE_BF16) return FA_ERR_UNSUPPORTED;
+    if (a->d_head != 64 && a->d_head != 128) return FA_ERR_UNSUPPORTED;
+    if (a->num_splits < 0 || a->num_splits > FA_MAX_SPLITS) return FA_ERR_UNSUPPORTED;
+    const long long bh = (long long)a->batch_size * a->num_heads;
+    if (bh > 65535) return FA_ERR_UNSUPPORTED;
+    if (!aligned16(a->q) || !aligned16(a->k) || !aligned16(a->v) || (a->o && !aligned16(a->o)))
+        return FA_ERR_MISALIGNED;
+    StaticScratchSetup* su = nullptr;
+    int rc = static_scratch_setup(&su);
+    if (rc != FA_OK) return rc;
+    if (su->cc_major != 10) return FA_ERR_NOT_SM100;
+
+    int splits = a->num_splits;
+    if (splits == 0) {          // same rule as fa_decode_default_splits, from the cached SM count
+        long long want = (8ll * su->sm_count + bh - 1) / bh;
+        long long max_by_len = a->seq_len_kv / 512 > 0 ? a->seq_len_kv / 512 : 1;
+        long long s = want < max_by_len ? want : max_by_len;
+        splits = (int)(s < 1 ? 1 : (s > FA_MAX_SPLITS ? FA_MAX_SPLITS : s));
+    }
+    if (splits > a->seq_len_kv) splits = a->seq_len_kv;
+    const int kps = (a->seq_len_kv + splits - 1) / splits;
+    splits = (a->seq_len_kv + kps - 1) / kps;
+    const size_t o_bytes = align256((size_t)bh * splits * a->d_head * sizeof(float));
+    const size_t l_bytes = align256((size_t)bh * splits * sizeof(float));
+    if (o_bytes + l_bytes > (size_t)FA_DECODE_STATIC_SCRATCH_BYTES) return FA_ERR_WORKSPACE;
+
+    float* o_part = static_cast<float*>(su->ptr);
+    float* lse_part = reinterpret_cast<float*>(static_cast<unsigned char*>(su->ptr) + o_bytes);
+    cudaStream_t stream = static_cast<cudaStream_t>(a->stream);
+    const dim3 grid(splits, (unsigned)bh);
+    const float sl2 = a->scale * kLog2e;
+    const uint16_t* q = static_cast<const uint16_t*>(a->q);
+    const uint16_t* k = static_cast<const uint16_t*>(a->k);
+    const uint16_t* v = static_cast<const uint16_t*>(a->v);
+    const bool bf = a->dtype == FA_DTYPE_BF16;
+#define FA_LAUNCH_DECODE_STATIC(DH, BF) \
+    decode_partial_kernel<DH, BF><<<grid, kDecodeWarps * 32, 0, stream>>>(q, k, v, o_part, lse_part, \
+        a->seq_len_kv, splits, kps, sl2)
+    if (a->d_head == 128) { if (bf) FA_LAUNCH_DECODE_STATIC(128, true); else FA_LAUNCH_DECODE_STATIC(128, false); }
+    else                  { if (bf) FA_LAUNCH_DECODE_STATIC(64, true);  else FA_LAUNCH_DECODE_STATIC(64, false); }
+#undef FA_LAUNCH_DECODE_STATIC
+    FA_CUDA_TRY(cudaGetLastError());
     return launch_combine(o_part, lse_part, splits, a->d_head, (long long)splits * a->d_head, 1, splits,
                           (int)bh, a->d_head, a->o, a->lse, a->o_f32, a->dtype, stream);
 }

@@ -124,6 +124,38 @@ int    fa_decode_default_splits(int batch_size, int num_heads, int seq_len_kv);
 int    fa_decode(const fa_decode_args* args);
 
 /*
+ * fa_decode without any allocation on either side.  (No counterpart in the
+ * reference, which has no decode path and allocates nothing per call.)
+ *
+ * Who needs it: hosts that hand the whole device to their own memory pool at
+ * start-up and forbid cudaMalloc afterwards (a serving runtime with a frozen
+ * arena, a plugin sandbox, a latency-critical loop where the device-wide
+ * synchronisation implied by cudaMalloc/cudaFree is not acceptable).  Such a
+ * caller cannot size and allocate the split-KV workspace fa_decode asks for.
+ *
+ * Here the per-split partial results live in an array built into the library
+ * image (FA_DECODE_STATIC_SCRATCH_BYTES of device memory, held by every GPU
+ * that loads the library until the process exits).  The caller passes inputs
+ * and outputs exactly as for fa_decode; `workspace` and `workspace_bytes` are
+ * ignored.  The call allocates nothing: no cudaMalloc, no cudaFree, no
+ * allocating library routine.
+ *
+ * Limit: batch_size*num_heads*splits*(d_head+1)*4 bytes (each part rounded up
+ * to 256) must fit in FA_DECODE_STATIC_SCRATCH_BYTES; beyond that the call
+ * launches nothing and returns FA_ERR_WORKSPACE.  Lower num_splits to fit.
+ *
+ * The first call on each device looks up the array's device address (once,
+ * with that device current); make that first call before starting any stream
+ * capture.  All calls on a device share the one array: it still holds the
+ * previous call's partials (every slot a call reads is first written by that
+ * call, so nothing needs clearing), and two calls whose kernels overlap on the
+ * GPU - different streams, or different host threads - race on it.  Serialise
+ * them, or use fa_decode with separate workspaces.
+ */
+#define FA_DECODE_STATIC_SCRATCH_BYTES (8u * 1024u * 1024u + 512u * 1024u)
+int fa_decode_static(const fa_decode_args* args);
+
+/*
  * LSE merge of n_parts partial results (the exchange step of KV-sequence
  * sharded decode: each rank's (o_f32, lse) gathered into one local buffer).
  *   o_parts  : fp32 [n_parts, rows, d_head]   lse_parts: fp32 [n_parts, rows]
