@@ -148,6 +148,54 @@ def cpu_reference_run(bh_sample: int, steps: int, warmup: int, threads: int):
     return kind, tflops, dt
 
 
+def reference_gpu_kernel_time(steps: int = 50):
+    """Same-box comparison line: the reference's own mma.sync kernel
+    (kernels/flash_attention.cu, recompiled unchanged for sm_100a into
+    oracle/_ref/libref_gpu.so) on the benchmark workload.  Returns None when
+    there is no GPU or the library was never built."""
+    import ctypes
+    from oracle import build_oracle
+    path = os.path.join(build_oracle.REF_OUT, "libref_gpu.so")
+    try:
+        import torch
+        if not (torch.cuda.is_available() and os.path.exists(path)):
+            return None
+    except Exception:
+        return None
+
+    class RefParams(ctypes.Structure):       # include/flash_attention.h:51-64 of the reference
+        _fields_ = [("Q", ctypes.c_void_p), ("K", ctypes.c_void_p), ("V", ctypes.c_void_p),
+                    ("O", ctypes.c_void_p), ("L", ctypes.c_void_p), ("batch_size", ctypes.c_int),
+                    ("num_heads", ctypes.c_int), ("seq_len", ctypes.c_int), ("d_head", ctypes.c_int),
+                    ("scale", ctypes.c_float), ("causal", ctypes.c_bool), ("stream", ctypes.c_void_p)]
+
+    lib = ctypes.CDLL(path, mode=ctypes.RTLD_LOCAL)
+    fn = getattr(lib, build_oracle.REF_LAUNCH_SYMBOL)
+    fn.restype = None
+    fn.argtypes = [ctypes.POINTER(RefParams)]
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda:0")
+    B, H, S, D = CFG["B"], CFG["H"], CFG["S"], CFG["D"]
+    q, k, v = (torch.randn((B * H, S, D), device=dev).to(torch.float16) for _ in range(3))
+    o = torch.empty_like(q)
+    lse = torch.empty((B * H, S), device=dev, dtype=torch.float32)
+    p = RefParams(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(), B, H, S, D,
+                  0.125, True, None)
+    for _ in range(5):
+        fn(ctypes.byref(p))
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(torch.cuda.default_stream())
+    for _ in range(steps):
+        fn(ctypes.byref(p))
+    e1.record(torch.cuda.default_stream())
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    return {"kernel": "reference flash_attention_ptx_kernel (mma.sync), -gencode arch=compute_100a,code=sm_100a",
+            "ms_per_step": ms, "tflops_causal_count": causal_flops(B * H, S, D) / (ms * 1e-3) / 1e12,
+            "tflops_refconv": refconv_flops(B * H, S, D) / (ms * 1e-3) / 1e12}
+
+
 def run_reference_arm(args, rank, world):
     if rank != 0:
         return
@@ -165,13 +213,17 @@ def run_reference_arm(args, rank, world):
         "n_gpus": args.gpus, "steps": steps, "warmup": warmup, "ms_per_step": dt * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
         "data": "synthetic: seeded iid N(0,1) rounded to fp16",
-        "config": {"workload": "causal prefill B8 H12 S2048 D64 (CPU: bounded sample of heads)"},
+        "config": {"workload": "causal prefill fp16 B=8 H=12 S=2048 D=64 scale=1/8, per GPU",
+                   "note": "CPU reference on a bounded sample of the workload's heads per step"},
         "cpu_baseline": {"value": tflops, "unit": "TFLOP/s (causal FLOP count)", "cores": cores,
                          "kind": kind, "sample": sample},
         "e2e": {"value": tflops, "unit": "TFLOP/s (causal FLOP count)", "h2d_bytes_per_step": 0,
                 "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
+    gpu_ref = reference_gpu_kernel_time()
+    if gpu_ref:
+        line["reference_gpu_kernel_on_this_gpu"] = gpu_ref   # information only; the arm's value is the CPU path
     print(json.dumps(line), flush=True)
 
 
@@ -289,6 +341,11 @@ def run_b200_arm(args, rank, local_rank, world):
     if not args.no_decode:
         decode = run_decode_bench(fa, torch, dev, stream, peaks, args)
 
+    # ---- KV-sequence-sharded decode: one long cache split over the ranks (N > 1 only)
+    kv_sharded = None
+    if world > 1 and not args.no_decode:
+        kv_sharded = run_kv_sharded_decode(fa, ge, torch, dist, dev, stream, rank, world, peaks, args)
+
     clocks = sampler.summary()
     cpu_baseline = None
     if rank == 0 and world == 1 and not args.no_cpu:
@@ -321,11 +378,54 @@ def run_b200_arm(args, rank, local_rank, world):
             line["strong_scaling_96_heads"] = strong
         if decode:
             line["decode"] = decode
+        if kv_sharded:
+            line["kv_sharded_decode"] = kv_sharded
         if cpu_baseline:
             line["cpu_baseline"] = cpu_baseline
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
+
+
+def run_kv_sharded_decode(fa, ge, torch, dist, dev, stream, rank, world, peaks, args):
+    """B=1 H=32 Skv=131072 D=128 fp16: each rank owns Skv/world keys, decodes its slice,
+    one NCCL all-gather of [H, D+1] fp32 per rank, fa_combine on every rank."""
+    sh = ge.load_module("sharding")
+    H, SKV, D = 32, 131072, 128
+    k0, kc = sh.kv_shard(SKV, rank, world)
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(5005 + rank)
+    k = torch.randn((H, kc, D), device=dev, dtype=torch.float32, generator=gen).to(torch.float16)
+    v = torch.randn((H, kc, D), device=dev, dtype=torch.float32, generator=gen).to(torch.float16)
+    gq = torch.Generator(device=dev)
+    gq.manual_seed(5004)
+    q = torch.randn((H, D), device=dev, dtype=torch.float32, generator=gq).to(torch.float16)
+    o = torch.empty((H, D), device=dev, dtype=torch.float16)
+    lse = torch.empty((H,), device=dev, dtype=torch.float32)
+    run = sh.ShardedDecode(fa, 1, H, D, kc, dtype="f16", num_splits=16)
+    scale = float(1.0 / np.sqrt(D))
+    steps = max(5, min(args.steps, 50))
+    for _ in range(5):
+        run(q, k, v, o, lse, scale, stream)
+    dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(steps):
+        run(q, k, v, o, lse, scale, stream)
+    e1.record(stream)
+    dist.barrier()
+    torch.cuda.synchronize()
+    t = torch.tensor([e0.elapsed_time(e1) / steps], device=dev, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+    total_bytes = 2 * H * SKV * D * 2
+    return {"workload": f"decode fp16 B=1 H={H} Skv={SKV} D={D}, keys sharded over {world} GPUs "
+                        f"({kc} per GPU), all-gather of {H * (D + 1) * 4} B per rank + combine",
+            "ms_per_step": ms, "aggregate_GBps": total_bytes / (ms * 1e-3) / 1e9,
+            "per_gpu_frac_of_hbm_peak": total_bytes / world / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
+            "note": "latency-bound: per-GPU traffic is tens of microseconds, the step is dominated by "
+                    "launches and the all-gather round trip", "scaling": "strong"}
 
 
 def run_decode_bench(fa, torch, dev, stream, peaks, args):
