@@ -83,37 +83,56 @@ __device__ long long g_cta_ts[4096][8];
 #define FA_CTS(k) do {} while (0)
 #endif
 
-template <int D, int BN, int NK, int NV>
+template <int D, int BN, int NK, int NV, bool FP8>
 struct PrefillSmem {
-    static constexpr int kNBox      = D / 64;              // 64-column (128-byte) boxes per row
+    static constexpr int kNBox      = D / 64;              // 64-column (128-byte) boxes per 16-bit row
     static constexpr int kQBoxBytes = kBM * 128;
     static constexpr int kKVBoxBytes = BN * 128;
-    static constexpr int kQBytes    = kNBox * kQBoxBytes;
-    static constexpr int kKVBytes   = kNBox * kKVBoxBytes;
-    static constexpr int kTotal     = kQBytes + (NK + NV) * kKVBytes + 1024;   // + alignment slack
+    // e4m3 rows of d_head 128 are exactly one 128-byte box.
+    static constexpr int kQBytes    = FP8 ? kQBoxBytes : kNBox * kQBoxBytes;
+    static constexpr int kKBytes    = FP8 ? kKVBoxBytes : kNBox * kKVBoxBytes;
+    static constexpr int kVBytes    = kNBox * kKVBoxBytes; // 16-bit V operand of P V (e4m3: converted copy)
+    static constexpr int kV8Bytes   = FP8 ? kKVBoxBytes : 0;   // landing buffer of the e4m3 V tile
+    static constexpr int kTotal     = kQBytes + NK * kKBytes + NV * kVBytes + kV8Bytes + 1024;
 };
 
-template <int D, int BN, int NK, int NV, bool CAUSAL, bool BF16>
+// Two e4m3 codes -> two fp16 values (exact).
+__device__ __forceinline__ uint32_t e4m3x2_to_f16x2(uint16_t v) {
+    uint32_t r;
+    asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(r) : "h"(v));
+    return r;
+}
+
+// FP8: Q, K, V are e4m3 codes with per-head scales.  S = Q K^T runs on the 8-bit tensor-core
+// kind; V is converted e4m3 -> fp16 in shared memory by warps 6-7 (exact) and P V runs on the
+// 16-bit kind with P in fp16, because an e4m3 P (3 mantissa bits) misses the output tolerance.
+// The Q and K scales fold into the softmax scale, the V scale into the final normalisation;
+// the output is bf16.
+template <int D, int BN, int NK, int NV, bool CAUSAL, bool BF16, bool FP8>
 __global__ void __launch_bounds__(kThreads, 2)
 prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o,
-               float* __restrict__ lse_out, int seq_len, int n_bh, int n_qtiles, float scale_log2,
-               int* status) {
+               float* __restrict__ lse_out, int seq_len, int n_bh, int n_qtiles, float scale_log2_in,
+               const float* __restrict__ q_scale, const float* __restrict__ k_scale,
+               const float* __restrict__ v_scale, int* status) {
     static_assert(BN == 128, "the softmax warps hold one full 128-column score row in registers");
-    using L = PrefillSmem<D, BN, NK, NV>;
+    static_assert(!FP8 || (D == 128 && NV == 1 && BF16), "e4m3 variant: d_head 128, bf16 output");
+    using L = PrefillSmem<D, BN, NK, NV, FP8>;
     constexpr int NBOX = L::kNBox;
     constexpr uint32_t S_COL = 0;
     constexpr uint32_t O_COL = 128;
     // D = 64: P has its own columns, so S is free as soon as the softmax warps hold it in
     // registers and the next Q K^T can be issued before P V.  D = 128: P reuses the S columns.
     constexpr bool EARLY_QK = (D == 64);
+    constexpr bool P_BF16 = BF16 && !FP8;                 // type of P (and of the V operand of P V)
     constexpr uint32_t P_COL = EARLY_QK ? 192 : 0;
     constexpr uint32_t TMEM_COLS = 256;
-    constexpr uint32_t FMT = BF16 ? kFmtBF16 : kFmtF16;
+    constexpr uint32_t FMT = P_BF16 ? kFmtBF16 : kFmtF16;
 
     extern __shared__ uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t bar_q, bar_s, bar_p, bar_o, bar_sfree;
     __shared__ __align__(8) uint64_t bar_kf[NK], bar_ke[NK], bar_vf[NV], bar_ve[NV];
+    __shared__ __align__(8) uint64_t bar_v8f, bar_v8e;    // e4m3 V landing buffer: filled / drained
     __shared__ uint32_t tmem_slot;
     __shared__ int abort_flag;
 
@@ -121,7 +140,9 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t q_s = base;
     const uint32_t k_s = q_s + L::kQBytes;
-    const uint32_t v_s = k_s + NK * L::kKVBytes;
+    const uint32_t v_s = k_s + NK * L::kKBytes;
+    const uint32_t v8_s = v_s + NV * L::kVBytes;
+    const uint32_t o_stage = FP8 ? v_s : q_s;             // epilogue staging: a dead operand buffer
     WaitCtl ctl{&abort_flag, status};
 
     // Heaviest query tiles first under the causal mask.
@@ -147,7 +168,9 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         mbar_init(smem_u32(&bar_sfree), 4);
         mbar_init(smem_u32(&bar_o), 1);
         for (int i = 0; i < NK; i++) { mbar_init(smem_u32(&bar_kf[i]), 1); mbar_init(smem_u32(&bar_ke[i]), 1); }
-        for (int i = 0; i < NV; i++) { mbar_init(smem_u32(&bar_vf[i]), 1); mbar_init(smem_u32(&bar_ve[i]), 1); }
+        for (int i = 0; i < NV; i++) { mbar_init(smem_u32(&bar_vf[i]), FP8 ? 64 : 1); mbar_init(smem_u32(&bar_ve[i]), 1); }
+        mbar_init(smem_u32(&bar_v8f), 1);
+        mbar_init(smem_u32(&bar_v8e), 64);
         abort_flag = 0;
         fence_mbar_init();
     }
@@ -167,25 +190,35 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsOther));
         if (warp == 4 && lane == 0) {
             // -------------------------------------------------------- TMA producer
+            constexpr int NLOAD = FP8 ? 1 : NBOX;         // boxes per Q / K tile
+            constexpr int XSTEP = FP8 ? 128 : 64;         // elements per box row
             mbar_arrive_expect_tx(smem_u32(&bar_q), L::kQBytes);
-            for (int b = 0; b < NBOX; b++)
-                tma_load_3d(q_s + b * L::kQBoxBytes, &tm_q, smem_u32(&bar_q), b * 64, q_start, bh);
+            for (int b = 0; b < NLOAD; b++)
+                tma_load_3d(q_s + b * L::kQBoxBytes, &tm_q, smem_u32(&bar_q), b * XSTEP, q_start, bh);
             for (int j = 0; j < n_kv; j++) {
                 const int sk = j % NK, sv = j % NV;
                 if (j >= NK && !mbar_wait(smem_u32(&bar_ke[sk]), ((j / NK) - 1) & 1, ctl, kBarKEmpty)) break;
-                mbar_arrive_expect_tx(smem_u32(&bar_kf[sk]), L::kKVBytes);
-                for (int b = 0; b < NBOX; b++)
-                    tma_load_3d(k_s + sk * L::kKVBytes + b * L::kKVBoxBytes, &tm_k,
-                                smem_u32(&bar_kf[sk]), b * 64, j * BN, bh);
-                if (j >= NV && !mbar_wait(smem_u32(&bar_ve[sv]), ((j / NV) - 1) & 1, ctl, kBarVEmpty)) break;
-                mbar_arrive_expect_tx(smem_u32(&bar_vf[sv]), L::kKVBytes);
-                for (int b = 0; b < NBOX; b++)
-                    tma_load_3d(v_s + sv * L::kKVBytes + b * L::kKVBoxBytes, &tm_v,
-                                smem_u32(&bar_vf[sv]), b * 64, j * BN, bh);
+                mbar_arrive_expect_tx(smem_u32(&bar_kf[sk]), L::kKBytes);
+                for (int b = 0; b < NLOAD; b++)
+                    tma_load_3d(k_s + sk * L::kKBytes + b * L::kKVBoxBytes, &tm_k,
+                                smem_u32(&bar_kf[sk]), b * XSTEP, j * BN, bh);
+                if constexpr (FP8) {
+                    // e4m3 V lands in its own buffer; warps 6-7 turn it into the fp16 operand.
+                    if (j >= 1 && !mbar_wait(smem_u32(&bar_v8e), (j - 1) & 1, ctl, kBarVEmpty)) break;
+                    mbar_arrive_expect_tx(smem_u32(&bar_v8f), L::kV8Bytes);
+                    tma_load_3d(v8_s, &tm_v, smem_u32(&bar_v8f), 0, j * BN, bh);
+                } else {
+                    if (j >= NV && !mbar_wait(smem_u32(&bar_ve[sv]), ((j / NV) - 1) & 1, ctl, kBarVEmpty)) break;
+                    mbar_arrive_expect_tx(smem_u32(&bar_vf[sv]), L::kVBytes);
+                    for (int b = 0; b < NBOX; b++)
+                        tma_load_3d(v_s + sv * L::kVBytes + b * L::kKVBoxBytes, &tm_v,
+                                    smem_u32(&bar_vf[sv]), b * 64, j * BN, bh);
+                }
             }
         } else if (warp == 5 && lane == 0) {
             // -------------------------------------------------------- MMA issuer
-            constexpr uint32_t idesc_qk = make_idesc(kBM, BN, FMT, FMT, kMajorK, kMajorK);
+            constexpr uint32_t QKFMT = FP8 ? kFmtE4M3 : FMT;
+            constexpr uint32_t idesc_qk = make_idesc(kBM, BN, QKFMT, QKFMT, kMajorK, kMajorK);
             constexpr uint32_t idesc_pv = make_idesc(kBM, D, FMT, FMT, kMajorK, kMajorMN);
             constexpr uint64_t hi_k = make_sdesc_hi(16, 1024);
             constexpr uint64_t hi_v = make_sdesc_hi(L::kKVBoxBytes, 1024);
@@ -196,13 +229,20 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                     !mbar_wait(smem_u32(&bar_sfree), (j - 1) & 1, ctl, kBarSFree)) return false;
                 tc_fence_after();
                 FA_TS(1, j, 0);
-                const uint32_t kb = k_s + sk * L::kKVBytes;
+                const uint32_t kb = k_s + sk * L::kKBytes;
+                if constexpr (FP8) {
 #pragma unroll
-                for (int kk = 0; kk < D / 16; kk++) {
-                    const uint32_t qo = (kk >> 2) * L::kQBoxBytes + (kk & 3) * 32;
-                    const uint32_t ko = (kk >> 2) * L::kKVBoxBytes + (kk & 3) * 32;
-                    mma_f16_ss(tmem + S_COL, make_sdesc(q_s + qo, hi_k), make_sdesc(kb + ko, hi_k),
-                               idesc_qk, kk > 0);
+                    for (int kk = 0; kk < D / 32; kk++)        // 32 e4m3 (32 bytes) of d_head per MMA
+                        mma_f8_ss(tmem + S_COL, make_sdesc(q_s + kk * 32, hi_k), make_sdesc(kb + kk * 32, hi_k),
+                                  idesc_qk, kk > 0);
+                } else {
+#pragma unroll
+                    for (int kk = 0; kk < D / 16; kk++) {
+                        const uint32_t qo = (kk >> 2) * L::kQBoxBytes + (kk & 3) * 32;
+                        const uint32_t ko = (kk >> 2) * L::kKVBoxBytes + (kk & 3) * 32;
+                        mma_f16_ss(tmem + S_COL, make_sdesc(q_s + qo, hi_k), make_sdesc(kb + ko, hi_k),
+                                   idesc_qk, kk > 0);
+                    }
                 }
                 tc_commit(smem_u32(&bar_s));
                 tc_commit(smem_u32(&bar_ke[sk]));
@@ -215,7 +255,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                 if (!mbar_wait(smem_u32(&bar_p), j & 1, ctl, kBarPFull)) return false;
                 tc_fence_after();
                 FA_TS(1, j, 2);
-                const uint32_t vb = v_s + sv * L::kKVBytes;
+                const uint32_t vb = v_s + sv * L::kVBytes;
 #pragma unroll
                 for (int kk = 0; kk < BN / 16; kk++)
                     mma_f16_ts(tmem + O_COL, tmem + P_COL + kk * 8, make_sdesc(vb + kk * 2048, hi_v),
@@ -236,6 +276,33 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             } else {
                 for (int j = 0; ok && j < n_kv; j++) ok = issue_qk(j) && issue_pv(j);
             }
+        } else if (FP8 && warp >= 6) {
+            // -------------------------------------------------------- e4m3 -> fp16 V converter
+            const int ct = tid - 192;                     // 0..63
+            for (int j = 0; j < n_kv; j++) {
+                bool w = mbar_wait(smem_u32(&bar_v8f), j & 1, ctl, kBarVFull);
+                // the fp16 copy of tile j-1 must have been consumed by P V(j-1)
+                if (j >= 1) w = w && mbar_wait(smem_u32(&bar_ve[0]), (j - 1) & 1, ctl, kBarVEmpty);
+                if (!__all_sync(0xffffffffu, w)) break;
+#pragma unroll 4
+                for (int it = 0; it < (BN * 16) / 64; it++) {
+                    const int g = ct + it * 64;           // 8-element group: row g/16, group-in-row g%16
+                    const int r = g >> 4, c8 = g & 15;
+                    const uint32_t src = v8_s + r * 128 + ((((c8 >> 1) ^ (r & 7))) << 4) + ((c8 & 1) << 3);
+                    uint32_t lo, hi;
+                    asm volatile("ld.shared.v2.b32 {%0, %1}, [%2];" : "=r"(lo), "=r"(hi) : "r"(src));
+                    const uint32_t w0 = e4m3x2_to_f16x2(static_cast<uint16_t>(lo & 0xFFFFu));
+                    const uint32_t w1 = e4m3x2_to_f16x2(static_cast<uint16_t>(lo >> 16));
+                    const uint32_t w2 = e4m3x2_to_f16x2(static_cast<uint16_t>(hi & 0xFFFFu));
+                    const uint32_t w3 = e4m3x2_to_f16x2(static_cast<uint16_t>(hi >> 16));
+                    const uint32_t dst = v_s + (c8 >> 3) * L::kKVBoxBytes + r * 128 + (((c8 & 7) ^ (r & 7)) << 4);
+                    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(w0), "r"(w1),
+                                 "r"(w2), "r"(w3) : "memory");
+                }
+                fence_proxy_async_smem();                 // the tensor core reads the copy through the async proxy
+                mbar_arrive(smem_u32(&bar_vf[0]));
+                mbar_arrive(smem_u32(&bar_v8e));
+            }
         }
         __syncwarp();
     } else {
@@ -249,6 +316,12 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         const uint32_t t_o = tmem + lane_off + O_COL;
         const int row_limit = CAUSAL ? min(seq_len, row + 1) : seq_len;   // keys [0,row_limit) visible
         const int tile_min_limit = CAUSAL ? min(seq_len, q_start + 1) : seq_len;
+        float scale_log2 = scale_log2_in;
+        float out_scale = 1.0f;
+        if constexpr (FP8) {
+            scale_log2 *= q_scale[bh] * k_scale[bh];
+            out_scale = v_scale[bh];
+        }
         const uint64_t scale2 = pack2(scale_log2, scale_log2);
         float m_used = 0.0f;
         uint64_t lsum2 = pack2(0.0f, 0.0f);              // running row sum, two partial lanes
@@ -329,7 +402,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                 unpack2(t, t0, t1);
                 const float p0 = ex2_approx(t0), p1 = ex2_approx(t1);
                 lsum2 = add2(lsum2, pack2(p0, p1));
-                pk[i] = pack_16<BF16>(p0, p1);
+                pk[i] = pack_16<P_BF16>(p0, p1);
             }
             if (!pv_prev_done) {
                 // P(j-1) must have been consumed by P V(j-1) before it is overwritten; by now it
@@ -358,7 +431,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             float l0, l1;
             unpack2(lsum2, l0, l1);
             const float l_run = l0 + l1;
-            const float inv_l = 1.0f / l_run;
+            const float inv_l = out_scale / l_run;
 #pragma unroll 1
             for (int c = 0; c < D / 32; c++) {
                 uint32_t t[32];
@@ -371,7 +444,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                         w[e] = pack_16<BF16>(__uint_as_float(t[g4 * 8 + 2 * e]) * inv_l,
                                              __uint_as_float(t[g4 * 8 + 2 * e + 1]) * inv_l);
                     const int g = c * 4 + g4;             // 8-element (16-byte) group index in the row
-                    const uint32_t addr = q_s + (g >> 3) * L::kQBoxBytes + r_in_tile * 128 +
+                    const uint32_t addr = o_stage + (g >> 3) * L::kQBoxBytes + r_in_tile * 128 +
                                           (((g & 7) ^ (r_in_tile & 7)) << 4);
                     asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w[0]),
                                  "r"(w[1]), "r"(w[2]), "r"(w[3])
@@ -385,7 +458,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         named_barrier_sync(1, 128);
         if (ok && tid == 0) {
             for (int b = 0; b < NBOX; b++)
-                tma_store_3d(&tm_o, q_s + b * L::kQBoxBytes, b * 64, q_start, bh);
+                tma_store_3d(&tm_o, o_stage + b * L::kQBoxBytes, b * 64, q_start, bh);
             tma_store_commit();
             tma_store_wait_read();        // the CTA may exit once the staging buffer has been read
         }
@@ -397,11 +470,11 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     if (warp == 5) tmem_dealloc(tmem, TMEM_COLS);
 }
 
-template <int D, int BN, int NK, int NV, bool CAUSAL, bool BF16>
+template <int D, int BN, int NK, int NV, bool CAUSAL, bool BF16, bool FP8 = false>
 int launch_instance(const fa_prefill_args& a, DeviceState* st, const CUtensorMap& tq,
                     const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& to) {
-    using L = PrefillSmem<D, BN, NK, NV>;
-    auto kernel = prefill_kernel<D, BN, NK, NV, CAUSAL, BF16>;
+    using L = PrefillSmem<D, BN, NK, NV, FP8>;
+    auto kernel = prefill_kernel<D, BN, NK, NV, CAUSAL, BF16, FP8>;
     static bool configured[64] = {};
     if (!configured[st->device]) {
         FA_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
@@ -412,7 +485,8 @@ int launch_instance(const fa_prefill_args& a, DeviceState* st, const CUtensorMap
     const long long n_cta = (long long)n_bh * n_qtiles;
     if (n_cta > 0x7FFFFFFFll) return FA_ERR_INVALID_ARGUMENT;
     kernel<<<(unsigned)n_cta, kThreads, L::kTotal, static_cast<cudaStream_t>(a.stream)>>>(
-        tq, tk, tv, to, a.lse, a.seq_len, n_bh, n_qtiles, a.scale * kLog2e, st->status);
+        tq, tk, tv, to, a.lse, a.seq_len, n_bh, n_qtiles, a.scale * kLog2e, a.q_scale, a.k_scale,
+        a.v_scale, st->status);
     FA_CUDA_TRY(cudaGetLastError());
     return FA_OK;
 }
@@ -449,7 +523,18 @@ extern "C" __attribute__((visibility("default"))) int fa_debug_cta_ts(long long*
 }
 #endif
 
-// Placeholder until the e4m3 kernel lands: reports the variant as not built.
-int launch_prefill_fp8(const fa_prefill_args&, DeviceState*) { return FA_ERR_UNSUPPORTED; }
+// e4m3 inputs (d_head 128), bf16 output.
+int launch_prefill_fp8(const fa_prefill_args& a, DeviceState* st) {
+    const uint64_t n_bh = (uint64_t)a.batch_size * a.num_heads;
+    constexpr int BN = 128;
+    CUtensorMap tq, tk, tv, to;
+    int rc;
+    if ((rc = make_tensor_map_3d(&tq, a.q, FA_DTYPE_E4M3, 128, a.seq_len, n_bh, 128, kBM)) != FA_OK) return rc;
+    if ((rc = make_tensor_map_3d(&tk, a.k, FA_DTYPE_E4M3, 128, a.seq_len, n_bh, 128, BN)) != FA_OK) return rc;
+    if ((rc = make_tensor_map_3d(&tv, a.v, FA_DTYPE_E4M3, 128, a.seq_len, n_bh, 128, BN)) != FA_OK) return rc;
+    if ((rc = make_tensor_map_3d(&to, a.o, FA_DTYPE_BF16, 128, a.seq_len, n_bh, 64, kBM)) != FA_OK) return rc;
+    if (a.causal) return launch_instance<128, BN, 2, 1, true, true, true>(a, st, tq, tk, tv, to);
+    return launch_instance<128, BN, 2, 1, false, true, true>(a, st, tq, tk, tv, to);
+}
 
 }  // namespace fa
