@@ -346,6 +346,11 @@ def run_b200_arm(args, rank, local_rank, world):
     if world > 1 and not args.no_decode:
         kv_sharded = run_kv_sharded_decode(fa, ge, torch, dist, dev, stream, rank, world, peaks, args)
 
+    # ---- the other BASELINE configurations (short runs, reported beside the headline)
+    other = None
+    if not args.no_extra:
+        other = run_other_configs(fa, torch, dev, stream, peaks)
+
     clocks = sampler.summary()
     cpu_baseline = None
     if rank == 0 and world == 1 and not args.no_cpu:
@@ -380,6 +385,8 @@ def run_b200_arm(args, rank, local_rank, world):
             line["decode"] = decode
         if kv_sharded:
             line["kv_sharded_decode"] = kv_sharded
+        if other:
+            line["other_configs"] = other
         if cpu_baseline:
             line["cpu_baseline"] = cpu_baseline
         print(json.dumps(line), flush=True)
@@ -426,6 +433,51 @@ def run_kv_sharded_decode(fa, ge, torch, dist, dev, stream, rank, world, peaks, 
             "per_gpu_frac_of_hbm_peak": total_bytes / world / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
             "note": "latency-bound: per-GPU traffic is tens of microseconds, the step is dominated by "
                     "launches and the all-gather round trip", "scaling": "strong"}
+
+
+def run_other_configs(fa, torch, dev, stream, peaks):
+    """Config 3 (bf16 B1 H32 S8192 D128, causal and not) and config 5 (e4m3 B8 H16 S4096 D128
+    causal): device-resident, 3 warm-up + 10 timed launches each, inputs 0.2-0.3 GB (> L2)."""
+    out = {}
+
+    def timed(fn, steps=10):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(steps):
+            fn()
+        e1.record(stream)
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / steps
+
+    bh, s, d = 32, 8192, 128
+    scale = float(1.0 / np.sqrt(d))
+    q, k, v = (torch.randn((bh, s, d), device=dev, dtype=torch.float32).to(torch.bfloat16) for _ in range(3))
+    o = torch.empty_like(q)
+    lse = torch.empty((bh, s), device=dev, dtype=torch.float32)
+    for causal in (True, False):
+        ms = timed(lambda: fa.prefill(q, k, v, o, lse, 1, bh, s, d, scale, causal, dtype="bf16", stream=stream))
+        flops = causal_flops(bh, s, d) if causal else refconv_flops(bh, s, d)
+        tf = flops / (ms * 1e-3) / 1e12
+        out["bf16_b1_h32_s8192_d128_" + ("causal" if causal else "noncausal")] = {
+            "ms": ms, "tflops": tf, "frac_of_measured_bf16_peak": tf / peaks["tflops"]}
+    del q, k, v, o, lse
+
+    bh, s, d = 128, 4096, 128
+    q8, k8, v8 = (torch.randn((bh, s, d), device=dev, dtype=torch.float32).to(torch.float8_e4m3fn).view(torch.uint8)
+                  for _ in range(3))
+    sc = torch.full((bh,), 0.01, device=dev, dtype=torch.float32)
+    o = torch.empty((bh, s, d), device=dev, dtype=torch.bfloat16)
+    lse = torch.empty((bh, s), device=dev, dtype=torch.float32)
+    ms = timed(lambda: fa.prefill(q8, k8, v8, o, lse, 8, 16, s, d, scale, True, dtype="e4m3", q_scale=sc,
+                                  k_scale=sc, v_scale=sc, stream=stream))
+    tf = causal_flops(bh, s, d) / (ms * 1e-3) / 1e12
+    out["e4m3_b8_h16_s4096_d128_causal"] = {"ms": ms, "tflops": tf,
+                                            "frac_of_measured_bf16_peak": tf / peaks["tflops"],
+                                            "note": "Q K^T on the 8-bit kind, P V on the 16-bit kind"}
+    return out
 
 
 def run_decode_bench(fa, torch, dev, stream, peaks, args):
@@ -480,6 +532,7 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-decode", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-extra", action="store_true", help="skip the long-context and FP8 configurations")
     ap.add_argument("--batch", type=int, default=0,
                     help="profiling only: override the prefill batch (the line is then not the headline)")
     ap.add_argument("--decode-batch", type=int, default=0,
