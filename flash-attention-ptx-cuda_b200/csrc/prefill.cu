@@ -1,4 +1,4 @@
-// Prefill forward kernel for sm_100a, 16-bit inputs (fp16 / bf16), d_head 64 or
+// Prefill forward kernel for sm_100a: fp16 / bf16 / e4m3 inputs, d_head 64 or
 // 128, causal or not, any sequence length.
 //
 // Replaces the reference's kernel and launcher
@@ -10,22 +10,39 @@
 // structure: no mma.sync, no ldmatrix, no cp.async, no block-wide barriers in
 // the loop.
 //
-// One CTA (8 warps) owns one 128-row query tile of one (batch, head):
-//   warp 4 (one lane)  TMA producer: Q once, then K and V tiles through two
-//                      mbarrier-guarded shared-memory rings (128-byte swizzle);
-//   warp 5 (one lane)  issues tcgen05.mma: S = Q K^T into TMEM, later
-//                      O += P V with P read from TMEM and V (MN-major) from
-//                      shared memory; completion is signalled by tcgen05.commit;
-//   warps 0-3          softmax: thread t owns query row t (TMEM lane t), reads
-//                      its S row with tcgen05.ld, keeps the running max / sum in
-//                      registers (no cross-thread reduction), writes P as packed
-//                      16-bit pairs with tcgen05.st, rescales O in TMEM only when
-//                      the max grew by more than 2^8, and in the epilogue
-//                      normalises O, stages it in swizzled shared memory and
-//                      stores it with one TMA store per 64 columns; LSE rows are
-//                      written as coalesced fp32.
-// Two CTAs fit on an SM (TMEM: 256 of 512 columns each), so one CTA's softmax
-// overlaps the other's tensor-core work.
+// Persistent kernel: one CTA of 16 warps per SM walks a list of work items (one
+// 128-row query tile of one (batch, head) each), heaviest first under the causal
+// mask, dealt to the CTAs in boustrophedon order so the per-CTA totals even out.
+//
+//   warps 8, 11        TMA producers (one lane each): Q per item and the K tiles / the V
+//   (one lane each)    tiles (128 keys) through mbarrier-guarded shared-memory rings,
+//                      128-byte swizzle.  K and V have a producer each so that K loads
+//                      are not held back behind the later-freed V slots.
+//   warp 9             issues S = Q K^T (tcgen05.mma, lane 0) into one of TWO score
+//                      buffers in TMEM; it runs up to two tiles ahead of the softmax
+//                      and only waits for a score buffer to be handed back.
+//   warp 10            issues O += P V: P from TMEM (one of two P buffers), V
+//                      (MN-major) from shared memory.  Q K^T and P V have an issuer
+//                      each because every tcgen05.mma / commit costs its issuing
+//                      thread ~50 clocks; one thread doing both was the bottleneck.
+//   warps 0-7          softmax, two groups of four warps.  Group 0 owns the even key
+//                      tiles (S0, P0), group 1 the odd ones (S1, P1), so the two
+//                      groups are in different phases of their tiles and keep the
+//                      MUFU pipe busy between them.  A thread owns a whole query row
+//                      (TMEM lane) of its tiles: one tcgen05.ld brings the 128 scores
+//                      into registers, no cross-thread reduction; p = 2^(s*scale*log2e
+//                      - m) with packed f32x2 arithmetic; P goes back to TMEM as
+//                      16-bit pairs.  The max in use is handed from tile to tile
+//                      through shared memory; it only moves (and O is only rescaled,
+//                      in TMEM) when a tile's max exceeds it by more than 2^8.
+//                      Epilogue per item: O / l -> 16-bit -> swizzled
+//                      staging -> TMA store (clipped per head); LSE as fp32.  The
+//                      tensor pipe already works on the next item meanwhile.
+//   warps 12-15        e4m3 only: turn each V tile into the fp16 operand of P V.
+//   (for 16-bit inputs warps 12-15 only donate registers.)
+//
+// TMEM (all 512 columns): S0 [0,128) S1 [128,256) O [256,256+D) P0 [384,448)
+// P1 [448,512).
 #include <cmath>
 
 #include "host_common.h"
@@ -35,17 +52,19 @@
 namespace fa {
 namespace {
 
-constexpr int kBM = 128;                 // query rows per CTA
-constexpr int kThreads = 256;            // warps 0-3 softmax, 4 TMA, 5 MMA, 6-7 only donate registers
-constexpr int kRegsSoftmax = 208;        // setmaxnreg targets: 128 * (208 + 48) = 256 * 128
-constexpr int kRegsOther = 48;
+constexpr int kBM = 128;                 // query rows per work item
+constexpr int kBN = 128;                 // keys per tile
+constexpr int kThreads = 512;            // 16 warps: 0-7 softmax, 8 TMA, 9 Q K^T issuer, 10 P V issuer, 12-15 e4m3 helper
+constexpr int kRegsSoftmax = 200;        // setmaxnreg targets: 256 * 200 + 256 * 56 = 512 * 128
+constexpr int kRegsOther = 56;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 constexpr float kRescaleThreshold = 8.0f;   // log2 units: rescale only if max grew > 2^8
 
 // Barrier ids reported in the status word when a wait gives up.
-enum : int { kBarQ = 1, kBarKFull = 2, kBarKEmpty = 3, kBarVFull = 4, kBarVEmpty = 5,
-             kBarSFull = 6, kBarPFull = 7, kBarOFull = 8, kBarSFree = 9 };
+enum : int { kBarQFull = 1, kBarQEmpty = 2, kBarKFull = 3, kBarKEmpty = 4, kBarVFull = 5,
+             kBarVEmpty = 6, kBarSFull = 7, kBarSFree = 8, kBarPFull = 9, kBarPV = 10,
+             kBarOFree = 11, kBarV8Full = 12, kBarV8Empty = 13, kBarM = 14, kBarEpi = 15, kBarODone = 16 };
 
 // Packed pairs of fp32 (sm_100 has two-wide fp32 FMA/ADD on 64-bit register pairs).
 __device__ __forceinline__ uint64_t pack2(float lo, float hi) {
@@ -71,31 +90,6 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
     asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
     return d;
 }
-
-#ifdef FA_PHASE_TIMING
-// Development aid (not compiled into the shipped library): per-tile clock stamps of one CTA.
-__device__ long long g_phase_ts[2][64][8];
-__device__ long long g_cta_ts[4096][8];
-#define FA_CTS(k) do { if (blockIdx.x < 4096) { g_cta_ts[blockIdx.x][k] = clock64(); } } while (0)
-#define FA_TS(who, j, k) do { if (blockIdx.x == FA_PHASE_TIMING && (j) < 64) g_phase_ts[who][j][k] = clock64(); } while (0)
-#else
-#define FA_TS(who, j, k) do {} while (0)
-#define FA_CTS(k) do {} while (0)
-#endif
-
-template <int D, int BN, int NK, int NV, bool FP8>
-struct PrefillSmem {
-    static constexpr int kNBox      = D / 64;              // 64-column (128-byte) boxes per 16-bit row
-    static constexpr int kQBoxBytes = kBM * 128;
-    static constexpr int kKVBoxBytes = BN * 128;
-    // e4m3 rows of d_head 128 are exactly one 128-byte box.
-    static constexpr int kQBytes    = FP8 ? kQBoxBytes : kNBox * kQBoxBytes;
-    static constexpr int kKBytes    = FP8 ? kKVBoxBytes : kNBox * kKVBoxBytes;
-    static constexpr int kVBytes    = kNBox * kKVBoxBytes; // 16-bit V operand of P V (e4m3: converted copy)
-    static constexpr int kV8Bytes   = FP8 ? kKVBoxBytes : 0;   // landing buffer of the e4m3 V tile
-    static constexpr int kTotal     = kQBytes + NK * kKBytes + NV * kVBytes + kV8Bytes + 1024;
-};
-
 // Two e4m3 codes -> two fp16 values (exact).
 __device__ __forceinline__ uint32_t e4m3x2_to_f16x2(uint16_t v) {
     uint32_t r;
@@ -103,36 +97,78 @@ __device__ __forceinline__ uint32_t e4m3x2_to_f16x2(uint16_t v) {
     return r;
 }
 
+#ifdef FA_PHASE_TIMING
+// Development aid (not compiled into the shipped library): clock stamps of one CTA.
+__device__ long long g_phase_ts[3][64][8];
+__device__ long long g_cta_ts[4096][8];
+#define FA_TS(who, j, k) do { if (blockIdx.x == FA_PHASE_TIMING && (j) < 64) g_phase_ts[who][j][k] = clock64(); } while (0)
+#define FA_CTS(i, k) do { if ((i) < 4096) { g_cta_ts[i][k] = clock64(); } } while (0)
+#else
+#define FA_TS(who, j, k) do {} while (0)
+#define FA_CTS(i, k) do {} while (0)
+#endif
+
+template <int D, bool FP8>
+struct PrefillSmem {
+    static constexpr int kNBox    = D / 64;               // 64-column (128-byte) boxes per 16-bit row
+    static constexpr int kBox     = 128 * 128;            // one box: 128 rows x 128 bytes
+    // e4m3 rows of d_head 128 are exactly one 128-byte box.
+    static constexpr int kQBytes  = FP8 ? kBox : kNBox * kBox;
+    static constexpr int kKBytes  = kQBytes;
+    static constexpr int kVBytes  = kNBox * kBox;         // 16-bit V operand of P V (e4m3: converted copy)
+    static constexpr int kV8Bytes = FP8 ? kBox : 0;       // landing buffers of the e4m3 V tiles
+    static constexpr int kOBytes  = kNBox * kBox;         // epilogue staging (16-bit output tile)
+    static constexpr int NK  = (D == 64) ? 4 : 2;
+    static constexpr int NV  = FP8 ? 1 : ((D == 64) ? 4 : 2);
+    static constexpr int NV8 = FP8 ? 2 : 0;
+    static constexpr int kTotal = kQBytes + NK * kKBytes + NV * kVBytes + NV8 * kV8Bytes + kOBytes + 1024;
+};
+
+// Work list: item index -> (query tile, head), heaviest first when causal.
+struct Item { int q_start, bh, n_kv; };
+
+template <bool CAUSAL>
+__device__ __forceinline__ bool get_item(int k, int n_items, int n_bh, int n_qtiles, int seq_len, Item& it) {
+    const int G = gridDim.x, c = blockIdx.x;
+    const int idx = (k & 1) ? k * G + (G - 1 - c) : k * G + c;     // boustrophedon deal
+    if (idx >= n_items) return false;
+    const int qt = CAUSAL ? (n_qtiles - 1 - idx / n_bh) : (idx / n_bh);
+    it.bh = idx % n_bh;
+    it.q_start = qt * kBM;
+    const int kv_len = CAUSAL ? min(seq_len, it.q_start + kBM) : seq_len;
+    it.n_kv = (kv_len + kBN - 1) / kBN;
+    return true;
+}
+
 // FP8: Q, K, V are e4m3 codes with per-head scales.  S = Q K^T runs on the 8-bit tensor-core
-// kind; V is converted e4m3 -> fp16 in shared memory by warps 6-7 (exact) and P V runs on the
+// kind; V is converted e4m3 -> fp16 in shared memory by warps 10-11 (exact) and P V runs on the
 // 16-bit kind with P in fp16, because an e4m3 P (3 mantissa bits) misses the output tolerance.
 // The Q and K scales fold into the softmax scale, the V scale into the final normalisation;
 // the output is bf16.
-template <int D, int BN, int NK, int NV, bool CAUSAL, bool BF16, bool FP8>
-__global__ void __launch_bounds__(kThreads, 2)
+template <int D, bool CAUSAL, bool BF16, bool FP8>
+__global__ void __launch_bounds__(kThreads, 1)
 prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o,
-               float* __restrict__ lse_out, int seq_len, int n_bh, int n_qtiles, float scale_log2_in,
-               const float* __restrict__ q_scale, const float* __restrict__ k_scale,
-               const float* __restrict__ v_scale, int* status) {
-    static_assert(BN == 128, "the softmax warps hold one full 128-column score row in registers");
-    static_assert(!FP8 || (D == 128 && NV == 1 && BF16), "e4m3 variant: d_head 128, bf16 output");
-    using L = PrefillSmem<D, BN, NK, NV, FP8>;
-    constexpr int NBOX = L::kNBox;
-    constexpr uint32_t S_COL = 0;
-    constexpr uint32_t O_COL = 128;
-    // D = 64: P has its own columns, so S is free as soon as the softmax warps hold it in
-    // registers and the next Q K^T can be issued before P V.  D = 128: P reuses the S columns.
-    constexpr bool EARLY_QK = (D == 64);
+               float* __restrict__ lse_out, int seq_len, int n_bh, int n_qtiles, int n_items,
+               float scale_log2_in, const float* __restrict__ q_scale,
+               const float* __restrict__ k_scale, const float* __restrict__ v_scale, int* status) {
+    static_assert(!FP8 || (D == 128 && BF16), "e4m3 variant: d_head 128, bf16 output");
+    using L = PrefillSmem<D, FP8>;
+    constexpr int NBOX = L::kNBox, NK = L::NK, NV = L::NV;
+    constexpr uint32_t O_COL = 256;
+    constexpr uint32_t TMEM_COLS = 512;
     constexpr bool P_BF16 = BF16 && !FP8;                 // type of P (and of the V operand of P V)
-    constexpr uint32_t P_COL = EARLY_QK ? 192 : 0;
-    constexpr uint32_t TMEM_COLS = 256;
     constexpr uint32_t FMT = P_BF16 ? kFmtBF16 : kFmtF16;
+    constexpr int DH = D / 2;                             // O columns per thread of a row pair
 
     extern __shared__ uint8_t smem_raw[];
-    __shared__ __align__(8) uint64_t bar_q, bar_s, bar_p, bar_o, bar_sfree;
+    __shared__ __align__(8) uint64_t bar_qf, bar_qe, bar_ofree, bar_odone;
     __shared__ __align__(8) uint64_t bar_kf[NK], bar_ke[NK], bar_vf[NV], bar_ve[NV];
-    __shared__ __align__(8) uint64_t bar_v8f, bar_v8e;    // e4m3 V landing buffer: filled / drained
+    __shared__ __align__(8) uint64_t bar_sf[2], bar_sfree[2], bar_pf[2], bar_pv[2];
+    __shared__ __align__(8) uint64_t bar_v8f[2], bar_v8e[2];
+    __shared__ __align__(8) uint64_t bar_m[2], bar_epi;      // softmax-internal hand-offs (bounded like the rest)
+    __shared__ float m_sh[128];                           // per row: the max in use, handed tile to tile
+    __shared__ float xm[2][128], xsum[2][128];            // per group and row: final reference max, partial sum
     __shared__ uint32_t tmem_slot;
     __shared__ int abort_flag;
 
@@ -142,339 +178,418 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     const uint32_t k_s = q_s + L::kQBytes;
     const uint32_t v_s = k_s + NK * L::kKBytes;
     const uint32_t v8_s = v_s + NV * L::kVBytes;
-    const uint32_t o_stage = FP8 ? v_s : q_s;             // epilogue staging: a dead operand buffer
+    const uint32_t o_s = v8_s + L::NV8 * L::kV8Bytes;
     WaitCtl ctl{&abort_flag, status};
 
-    // Heaviest query tiles first under the causal mask.
-    const int work = blockIdx.x;
-    const int qt = CAUSAL ? (n_qtiles - 1 - work / n_bh) : (work / n_bh);
-    const int bh = work % n_bh;
-    const int q_start = qt * kBM;
-    const int kv_len = CAUSAL ? min(seq_len, q_start + kBM) : seq_len;
-    const int n_kv = (kv_len + BN - 1) / BN;
-
-#ifdef FA_PHASE_TIMING
-    if (tid == 0 && blockIdx.x < 4096) {
-        unsigned smid; asm volatile("mov.u32 %0, %smid;" : "=r"(smid));
-        g_cta_ts[blockIdx.x][6] = smid;
-        g_cta_ts[blockIdx.x][7] = (long long)global_timer_ns();
-    }
-#endif
-    if (tid == 0) FA_CTS(0);
     if (tid == 0) {
-        mbar_init(smem_u32(&bar_q), 1);
-        mbar_init(smem_u32(&bar_s), 1);
-        mbar_init(smem_u32(&bar_p), 4);          // one arrival per softmax warp
-        mbar_init(smem_u32(&bar_sfree), 4);
-        mbar_init(smem_u32(&bar_o), 1);
+        mbar_init(smem_u32(&bar_qf), 1);
+        mbar_init(smem_u32(&bar_qe), 1);
+        mbar_init(smem_u32(&bar_ofree), 8);
+        mbar_init(smem_u32(&bar_odone), 1);
         for (int i = 0; i < NK; i++) { mbar_init(smem_u32(&bar_kf[i]), 1); mbar_init(smem_u32(&bar_ke[i]), 1); }
-        for (int i = 0; i < NV; i++) { mbar_init(smem_u32(&bar_vf[i]), FP8 ? 64 : 1); mbar_init(smem_u32(&bar_ve[i]), 1); }
-        mbar_init(smem_u32(&bar_v8f), 1);
-        mbar_init(smem_u32(&bar_v8e), 64);
+        for (int i = 0; i < NV; i++) { mbar_init(smem_u32(&bar_vf[i]), FP8 ? 128 : 1); mbar_init(smem_u32(&bar_ve[i]), 1); }
+        for (int i = 0; i < 2; i++) {
+            mbar_init(smem_u32(&bar_sf[i]), 1);
+            mbar_init(smem_u32(&bar_sfree[i]), 4);       // one arrival per warp of the owning group
+            mbar_init(smem_u32(&bar_pf[i]), 4);
+            mbar_init(smem_u32(&bar_pv[i]), 1);
+            mbar_init(smem_u32(&bar_v8f[i]), 1);
+            mbar_init(smem_u32(&bar_v8e[i]), 128);
+        }
+        for (int i = 0; i < 2; i++) mbar_init(smem_u32(&bar_m[i]), 4);   // a group published its tile's max
+        mbar_init(smem_u32(&bar_epi), 8);
         abort_flag = 0;
         fence_mbar_init();
     }
-    if (warp == 4 && lane == 0) {
+    if (warp == 8 && lane == 0) {
         prefetch_tensormap(&tm_q); prefetch_tensormap(&tm_k);
         prefetch_tensormap(&tm_v); prefetch_tensormap(&tm_o);
     }
     __syncthreads();
-    if (warp == 5) tmem_alloc(smem_u32(&tmem_slot), TMEM_COLS);
+    if (warp == 9) tmem_alloc(smem_u32(&tmem_slot), TMEM_COLS);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = tmem_slot;
-    if (tid == 0) FA_CTS(1);
+    const int n_rounds = (n_items + gridDim.x - 1) / gridDim.x;
 
-    if (warp >= 4) {
-        asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsOther));
-        if (warp == 4 && lane == 0) {
-            // -------------------------------------------------------- TMA producer
+    if (warp >= 8) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsOther));
+    if (warp == 8) {
+        // ------------------------------------------------------------ TMA producer: Q and K
+        // (K and V have a producer each: a K slot frees when its Q K^T is done, a V slot only when
+        // its P V is done, much later; one in-order producer would hold K loads back behind V.)
+        if (lane == 0) {
             constexpr int NLOAD = FP8 ? 1 : NBOX;         // boxes per Q / K tile
             constexpr int XSTEP = FP8 ? 128 : 64;         // elements per box row
-            mbar_arrive_expect_tx(smem_u32(&bar_q), L::kQBytes);
-            for (int b = 0; b < NLOAD; b++)
-                tma_load_3d(q_s + b * L::kQBoxBytes, &tm_q, smem_u32(&bar_q), b * XSTEP, q_start, bh);
-            for (int j = 0; j < n_kv; j++) {
-                const int sk = j % NK, sv = j % NV;
-                if (j >= NK && !mbar_wait(smem_u32(&bar_ke[sk]), ((j / NK) - 1) & 1, ctl, kBarKEmpty)) break;
-                mbar_arrive_expect_tx(smem_u32(&bar_kf[sk]), L::kKBytes);
+            int g = 0, it_n = 0;
+            bool ok = true;
+            for (int r = 0; ok && r < n_rounds; r++) {
+                Item it;
+                if (!get_item<CAUSAL>(r, n_items, n_bh, n_qtiles, seq_len, it)) continue;
+                if (it_n > 0 && !mbar_wait(smem_u32(&bar_qe), (it_n - 1) & 1, ctl, kBarQEmpty)) break;
+                mbar_arrive_expect_tx(smem_u32(&bar_qf), L::kQBytes);
                 for (int b = 0; b < NLOAD; b++)
-                    tma_load_3d(k_s + sk * L::kKBytes + b * L::kKVBoxBytes, &tm_k,
-                                smem_u32(&bar_kf[sk]), b * XSTEP, j * BN, bh);
-                if constexpr (FP8) {
-                    // e4m3 V lands in its own buffer; warps 6-7 turn it into the fp16 operand.
-                    if (j >= 1 && !mbar_wait(smem_u32(&bar_v8e), (j - 1) & 1, ctl, kBarVEmpty)) break;
-                    mbar_arrive_expect_tx(smem_u32(&bar_v8f), L::kV8Bytes);
-                    tma_load_3d(v8_s, &tm_v, smem_u32(&bar_v8f), 0, j * BN, bh);
-                } else {
-                    if (j >= NV && !mbar_wait(smem_u32(&bar_ve[sv]), ((j / NV) - 1) & 1, ctl, kBarVEmpty)) break;
-                    mbar_arrive_expect_tx(smem_u32(&bar_vf[sv]), L::kVBytes);
-                    for (int b = 0; b < NBOX; b++)
-                        tma_load_3d(v_s + sv * L::kVBytes + b * L::kKVBoxBytes, &tm_v,
-                                    smem_u32(&bar_vf[sv]), b * 64, j * BN, bh);
+                    tma_load_3d(q_s + b * L::kBox, &tm_q, smem_u32(&bar_qf), b * XSTEP, it.q_start, it.bh);
+                for (int j = 0; j < it.n_kv; j++, g++) {
+                    const int sk = g % NK;
+                    if (g >= NK && !mbar_wait(smem_u32(&bar_ke[sk]), ((g / NK) - 1) & 1, ctl, kBarKEmpty)) { ok = false; break; }
+                    mbar_arrive_expect_tx(smem_u32(&bar_kf[sk]), L::kKBytes);
+                    for (int b = 0; b < NLOAD; b++)
+                        tma_load_3d(k_s + sk * L::kKBytes + b * L::kBox, &tm_k, smem_u32(&bar_kf[sk]),
+                                    b * XSTEP, j * kBN, it.bh);
+                }
+                it_n++;
+            }
+        }
+        __syncwarp();
+    } else if (warp == 11) {
+        // ------------------------------------------------------------ TMA producer: V
+        if (lane == 0) {
+            int g = 0;
+            bool ok = true;
+            for (int r = 0; ok && r < n_rounds; r++) {
+                Item it;
+                if (!get_item<CAUSAL>(r, n_items, n_bh, n_qtiles, seq_len, it)) continue;
+                for (int j = 0; j < it.n_kv; j++, g++) {
+                    if constexpr (FP8) {
+                        // e4m3 V lands in its own buffers; warps 12-15 turn it into the fp16 operand.
+                        const int s8 = g & 1;
+                        if (g >= 2 && !mbar_wait(smem_u32(&bar_v8e[s8]), ((g >> 1) - 1) & 1, ctl, kBarV8Empty)) { ok = false; break; }
+                        mbar_arrive_expect_tx(smem_u32(&bar_v8f[s8]), L::kV8Bytes);
+                        tma_load_3d(v8_s + s8 * L::kV8Bytes, &tm_v, smem_u32(&bar_v8f[s8]), 0, j * kBN, it.bh);
+                    } else {
+                        const int sv = g % NV;
+                        if (g >= NV && !mbar_wait(smem_u32(&bar_ve[sv]), ((g / NV) - 1) & 1, ctl, kBarVEmpty)) { ok = false; break; }
+                        mbar_arrive_expect_tx(smem_u32(&bar_vf[sv]), L::kVBytes);
+                        for (int b = 0; b < NBOX; b++)
+                            tma_load_3d(v_s + sv * L::kVBytes + b * L::kBox, &tm_v, smem_u32(&bar_vf[sv]),
+                                        b * 64, j * kBN, it.bh);
+                    }
                 }
             }
-        } else if (warp == 5 && lane == 0) {
-            // -------------------------------------------------------- MMA issuer
-            constexpr uint32_t QKFMT = FP8 ? kFmtE4M3 : FMT;
-            constexpr uint32_t idesc_qk = make_idesc(kBM, BN, QKFMT, QKFMT, kMajorK, kMajorK);
-            constexpr uint32_t idesc_pv = make_idesc(kBM, D, FMT, FMT, kMajorK, kMajorMN);
-            constexpr uint64_t hi_k = make_sdesc_hi(16, 1024);
-            constexpr uint64_t hi_v = make_sdesc_hi(L::kKVBoxBytes, 1024);
-            auto issue_qk = [&](int j) -> bool {
-                const int sk = j % NK;
-                if (!mbar_wait(smem_u32(&bar_kf[sk]), (j / NK) & 1, ctl, kBarKFull)) return false;
-                if (EARLY_QK && j > 0 &&
-                    !mbar_wait(smem_u32(&bar_sfree), (j - 1) & 1, ctl, kBarSFree)) return false;
+        }
+        __syncwarp();
+    } else if (warp == 9) {
+        // ------------------------------------------------------------ Q K^T issuer
+        // The whole warp walks the loop (uniform control flow keeps the descriptors in uniform
+        // registers); lane 0 issues.  A tcgen05.mma or commit costs the issuing thread ~50 clocks,
+        // so Q K^T and P V have an issuer warp each: this one never waits for the softmax of a
+        // tile, only for its score buffer to be handed back.
+        constexpr uint32_t QKFMT = FP8 ? kFmtE4M3 : FMT;
+        constexpr uint32_t idesc_qk = make_idesc(kBM, kBN, QKFMT, QKFMT, kMajorK, kMajorK);
+        constexpr uint64_t hi_k = make_sdesc_hi(16, 1024);
+        int g = 0, it_n = 0;
+        bool ok = true;
+        for (int r = 0; ok && r < n_rounds; r++) {
+            Item it;
+            if (!get_item<CAUSAL>(r, n_items, n_bh, n_qtiles, seq_len, it)) continue;
+            if (!mbar_wait(smem_u32(&bar_qf), it_n & 1, ctl, kBarQFull)) break;
+            for (int j = 0; j < it.n_kv; j++, g++) {
+                const int b = g & 1, sk = g % NK;
+                if (!mbar_wait(smem_u32(&bar_kf[sk]), (g / NK) & 1, ctl, kBarKFull)) { ok = false; break; }
+                // the score buffer was last used by tile g-2: the softmax warps must hold it in registers
+                if (g >= 2 && !mbar_wait(smem_u32(&bar_sfree[b]), ((g >> 1) - 1) & 1, ctl, kBarSFree)) { ok = false; break; }
                 tc_fence_after();
-                FA_TS(1, j, 0);
+                if (r == 0 && lane == 0) FA_TS(1, j, 0);
                 const uint32_t kb = k_s + sk * L::kKBytes;
+                const uint32_t sc = tmem + b * 128;
                 if constexpr (FP8) {
 #pragma unroll
-                    for (int kk = 0; kk < D / 32; kk++)        // 32 e4m3 (32 bytes) of d_head per MMA
-                        mma_f8_ss(tmem + S_COL, make_sdesc(q_s + kk * 32, hi_k), make_sdesc(kb + kk * 32, hi_k),
-                                  idesc_qk, kk > 0);
+                    for (int kk = 0; kk < D / 32; kk++) {         // 32 e4m3 (32 bytes) of d_head per MMA
+                        const uint64_t da = make_sdesc(q_s + kk * 32, hi_k), db = make_sdesc(kb + kk * 32, hi_k);
+                        if (lane == 0) mma_f8_ss(sc, da, db, idesc_qk, kk > 0);
+                    }
                 } else {
 #pragma unroll
                     for (int kk = 0; kk < D / 16; kk++) {
-                        const uint32_t qo = (kk >> 2) * L::kQBoxBytes + (kk & 3) * 32;
-                        const uint32_t ko = (kk >> 2) * L::kKVBoxBytes + (kk & 3) * 32;
-                        mma_f16_ss(tmem + S_COL, make_sdesc(q_s + qo, hi_k), make_sdesc(kb + ko, hi_k),
-                                   idesc_qk, kk > 0);
+                        const uint32_t off = (kk >> 2) * L::kBox + (kk & 3) * 32;
+                        const uint64_t da = make_sdesc(q_s + off, hi_k), db = make_sdesc(kb + off, hi_k);
+                        if (lane == 0) mma_f16_ss(sc, da, db, idesc_qk, kk > 0);
                     }
                 }
-                tc_commit(smem_u32(&bar_s));
-                tc_commit(smem_u32(&bar_ke[sk]));
-                FA_TS(1, j, 1);
-                return true;
-            };
-            auto issue_pv = [&](int j) -> bool {
-                const int sv = j % NV;
-                if (!mbar_wait(smem_u32(&bar_vf[sv]), (j / NV) & 1, ctl, kBarVFull)) return false;
-                if (!mbar_wait(smem_u32(&bar_p), j & 1, ctl, kBarPFull)) return false;
-                tc_fence_after();
-                FA_TS(1, j, 2);
-                const uint32_t vb = v_s + sv * L::kVBytes;
-#pragma unroll
-                for (int kk = 0; kk < BN / 16; kk++)
-                    mma_f16_ts(tmem + O_COL, tmem + P_COL + kk * 8, make_sdesc(vb + kk * 2048, hi_v),
-                               idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
-                tc_commit(smem_u32(&bar_o));
-                tc_commit(smem_u32(&bar_ve[sv]));
-                FA_TS(1, j, 3);
-                return true;
-            };
-            bool ok = mbar_wait(smem_u32(&bar_q), 0, ctl, kBarQ);
-            if (EARLY_QK) {
-                // S(j+1) is computed while the softmax warps still work on S(j).
-                ok = ok && issue_qk(0);
-                for (int j = 0; ok && j < n_kv; j++) {
-                    if (j + 1 < n_kv) ok = issue_qk(j + 1);
-                    ok = ok && issue_pv(j);
+                if (lane == 0) {
+                    tc_commit(smem_u32(&bar_sf[b]));
+                    tc_commit(smem_u32(&bar_ke[sk]));
+                    if (j == it.n_kv - 1) tc_commit(smem_u32(&bar_qe));   // Q is dead after the item's last Q K^T
                 }
-            } else {
-                for (int j = 0; ok && j < n_kv; j++) ok = issue_qk(j) && issue_pv(j);
+                __syncwarp();
+                if (r == 0 && lane == 0) FA_TS(1, j, 1);
             }
-        } else if (FP8 && warp >= 6) {
-            // -------------------------------------------------------- e4m3 -> fp16 V converter
-            const int ct = tid - 192;                     // 0..63
-            for (int j = 0; j < n_kv; j++) {
-                bool w = mbar_wait(smem_u32(&bar_v8f), j & 1, ctl, kBarVFull);
-                // the fp16 copy of tile j-1 must have been consumed by P V(j-1)
-                if (j >= 1) w = w && mbar_wait(smem_u32(&bar_ve[0]), (j - 1) & 1, ctl, kBarVEmpty);
-                if (!__all_sync(0xffffffffu, w)) break;
-#pragma unroll 4
-                for (int it = 0; it < (BN * 16) / 64; it++) {
-                    const int g = ct + it * 64;           // 8-element group: row g/16, group-in-row g%16
-                    const int r = g >> 4, c8 = g & 15;
-                    const uint32_t src = v8_s + r * 128 + ((((c8 >> 1) ^ (r & 7))) << 4) + ((c8 & 1) << 3);
-                    uint32_t lo, hi;
-                    asm volatile("ld.shared.v2.b32 {%0, %1}, [%2];" : "=r"(lo), "=r"(hi) : "r"(src));
-                    const uint32_t w0 = e4m3x2_to_f16x2(static_cast<uint16_t>(lo & 0xFFFFu));
-                    const uint32_t w1 = e4m3x2_to_f16x2(static_cast<uint16_t>(lo >> 16));
-                    const uint32_t w2 = e4m3x2_to_f16x2(static_cast<uint16_t>(hi & 0xFFFFu));
-                    const uint32_t w3 = e4m3x2_to_f16x2(static_cast<uint16_t>(hi >> 16));
-                    const uint32_t dst = v_s + (c8 >> 3) * L::kKVBoxBytes + r * 128 + (((c8 & 7) ^ (r & 7)) << 4);
-                    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(w0), "r"(w1),
-                                 "r"(w2), "r"(w3) : "memory");
+            it_n++;
+        }
+    } else if (warp == 10) {
+        // ------------------------------------------------------------ P V issuer
+        constexpr uint32_t idesc_pv = make_idesc(kBM, D, FMT, FMT, kMajorK, kMajorMN);
+        constexpr uint64_t hi_v = make_sdesc_hi(L::kBox, 1024);
+        int g = 0, it_n = 0;
+        bool ok = true;
+        for (int r = 0; ok && r < n_rounds; r++) {
+            Item it;
+            if (!get_item<CAUSAL>(r, n_items, n_bh, n_qtiles, seq_len, it)) continue;
+            for (int j = 0; j < it.n_kv; j++, g++) {
+                const int b = g & 1, sv = g % NV;
+                if (!mbar_wait(smem_u32(&bar_vf[sv]), (g / NV) & 1, ctl, kBarVFull)) { ok = false; break; }
+                if (!mbar_wait(smem_u32(&bar_pf[b]), (g >> 1) & 1, ctl, kBarPFull)) { ok = false; break; }
+                // the first P V of an item overwrites O: the previous item's epilogue must have read it
+                if (j == 0 && it_n > 0 && !mbar_wait(smem_u32(&bar_ofree), (it_n - 1) & 1, ctl, kBarOFree)) { ok = false; break; }
+                tc_fence_after();
+                if (r == 0 && lane == 0) FA_TS(1, j, 2);
+                const uint32_t vb = v_s + sv * L::kVBytes;
+                const uint32_t pc = tmem + 384 + b * 64;
+#pragma unroll
+                for (int kk = 0; kk < kBN / 16; kk++) {
+                    const uint64_t db = make_sdesc(vb + kk * 2048, hi_v);
+                    if (lane == 0) mma_f16_ts(tmem + O_COL, pc + kk * 8, db, idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
                 }
-                fence_proxy_async_smem();                 // the tensor core reads the copy through the async proxy
-                mbar_arrive(smem_u32(&bar_vf[0]));
-                mbar_arrive(smem_u32(&bar_v8e));
+                if (lane == 0) {
+                    tc_commit(smem_u32(&bar_pv[b]));
+                    tc_commit(smem_u32(&bar_ve[sv]));
+                    if (j == it.n_kv - 1) tc_commit(smem_u32(&bar_odone));   // the item's O is complete
+                }
+                __syncwarp();
+                if (r == 0 && lane == 0) FA_TS(1, j, 3);
+            }
+            it_n++;
+        }
+    } else if (warp >= 12) {
+        if constexpr (FP8) {
+            // -------------------------------------------------------- e4m3 -> fp16 V converter
+            const int ct = tid - 384;                     // 0..127
+            int g = 0;
+            bool ok = true;
+            for (int r = 0; ok && r < n_rounds; r++) {
+                Item it;
+                if (!get_item<CAUSAL>(r, n_items, n_bh, n_qtiles, seq_len, it)) continue;
+                for (int j = 0; j < it.n_kv; j++, g++) {
+                    const int s8 = g & 1;
+                    bool w = mbar_wait(smem_u32(&bar_v8f[s8]), (g >> 1) & 1, ctl, kBarV8Full);
+                    // the fp16 copy of tile g-1 must have been consumed by its P V
+                    if (g >= 1) w = w && mbar_wait(smem_u32(&bar_ve[0]), (g - 1) & 1, ctl, kBarVEmpty);
+                    if (!__all_sync(0xffffffffu, w)) { ok = false; break; }
+                    const uint32_t src_base = v8_s + s8 * L::kV8Bytes;
+#pragma unroll 4
+                    for (int i = 0; i < (kBN * 16) / 128; i++) {
+                        const int c16 = ct + i * 128;         // 8-element group: row c16/16, group-in-row c16%16
+                        const int rr = c16 >> 4, c8 = c16 & 15;
+                        const uint32_t src = src_base + rr * 128 + (((c8 >> 1) ^ (rr & 7)) << 4) + ((c8 & 1) << 3);
+                        uint32_t lo, hi;
+                        asm volatile("ld.shared.v2.b32 {%0, %1}, [%2];" : "=r"(lo), "=r"(hi) : "r"(src));
+                        const uint32_t w0 = e4m3x2_to_f16x2(static_cast<uint16_t>(lo & 0xFFFFu));
+                        const uint32_t w1 = e4m3x2_to_f16x2(static_cast<uint16_t>(lo >> 16));
+                        const uint32_t w2 = e4m3x2_to_f16x2(static_cast<uint16_t>(hi & 0xFFFFu));
+                        const uint32_t w3 = e4m3x2_to_f16x2(static_cast<uint16_t>(hi >> 16));
+                        const uint32_t dst = v_s + (c8 >> 3) * L::kBox + rr * 128 + (((c8 & 7) ^ (rr & 7)) << 4);
+                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(w0), "r"(w1),
+                                     "r"(w2), "r"(w3) : "memory");
+                    }
+                    fence_proxy_async_smem();             // the tensor core reads the copy through the async proxy
+                    mbar_arrive(smem_u32(&bar_vf[0]));
+                    mbar_arrive(smem_u32(&bar_v8e[s8]));
+                }
             }
         }
         __syncwarp();
     } else {
+        // ------------------------------------------------------------ softmax + epilogue (warps 0-7)
         asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegsSoftmax));
-        // ------------------------------------------------------------ softmax + epilogue
-        const int r_in_tile = tid;                       // 0..127 == TMEM lane
-        const int row = q_start + r_in_tile;
-        const uint32_t lane_off = static_cast<uint32_t>(warp * 32) << 16;
-        const uint32_t t_s = tmem + lane_off + S_COL;
-        const uint32_t t_p = tmem + lane_off + P_COL;
+        const int grp = warp >> 2;                        // group 0 owns even tiles (S0, P0), group 1 odd ones
+        const int r_in_tile = (warp & 3) * 32 + lane;     // 0..127 == TMEM lane; one thread owns the whole row
+        const uint32_t lane_off = static_cast<uint32_t>((warp & 3) * 32) << 16;
+        const uint32_t t_s = tmem + lane_off + grp * 128;
+        const uint32_t t_p = tmem + lane_off + 384 + grp * 64;
         const uint32_t t_o = tmem + lane_off + O_COL;
-        const int row_limit = CAUSAL ? min(seq_len, row + 1) : seq_len;   // keys [0,row_limit) visible
-        const int tile_min_limit = CAUSAL ? min(seq_len, q_start + 1) : seq_len;
-        float scale_log2 = scale_log2_in;
-        float out_scale = 1.0f;
-        if constexpr (FP8) {
-            scale_log2 *= q_scale[bh] * k_scale[bh];
-            out_scale = v_scale[bh];
-        }
-        const uint64_t scale2 = pack2(scale_log2, scale_log2);
-        float m_used = 0.0f;
-        uint64_t lsum2 = pack2(0.0f, 0.0f);              // running row sum, two partial lanes
+        // Rendezvous of softmax warps on an mbarrier (one arrival per warp); makes the shared-memory
+        // writes of every lane before it visible to every lane after it.
+        auto rendezvous = [&](uint32_t bar, uint32_t parity, int id) -> bool {
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar);
+            return __all_sync(0xffffffffu, mbar_wait(bar, parity, ctl, id));
+        };
+        int g0 = 0, it_n = 0;
         bool ok = true;
 
-        for (int j = 0; j < n_kv; j++) {
-            const int kv_start = j * BN;
-            // The votes keep the warp together: every lane leaves the loop or none does.
-            if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&bar_s), j & 1, ctl, kBarSFull))) { ok = false; break; }
-            tc_fence_after();
-            if (tid == 0) FA_TS(0, j, 0);
-            if (tid == 0 && j == 0) FA_CTS(2);
-            uint32_t s[128];
-            tmem_ld128_wait(t_s, s);
-            if (tid == 0) FA_TS(0, j, 1);
-            if (EARLY_QK) {                              // S is in registers: release the TMEM columns
+        for (int r = 0; ok && r < n_rounds; r++) {
+            Item it;
+            if (!get_item<CAUSAL>(r, n_items, n_bh, n_qtiles, seq_len, it)) continue;
+            const int row = it.q_start + r_in_tile;
+            const int row_limit = CAUSAL ? min(seq_len, row + 1) : seq_len;   // keys [0,row_limit) visible
+            const int tile_min_limit = CAUSAL ? min(seq_len, it.q_start + 1) : seq_len;
+            float scale_log2 = scale_log2_in, out_scale = 1.0f;
+            if constexpr (FP8) {
+                scale_log2 *= q_scale[it.bh] * k_scale[it.bh];
+                out_scale = v_scale[it.bh];
+            }
+            const uint64_t scale2 = pack2(scale_log2, scale_log2);
+            // Running state of THIS thread: the reference max its partial row sum is expressed in.
+            // The row's two threads alternate tiles; the max in use travels from tile to tile
+            // through m_sh, so every tile of a row is exponentiated against one agreed sequence.
+            float m_mine = -1e30f;
+            uint64_t lsum2 = pack2(0.0f, 0.0f);
+            if (tid == 0) FA_CTS(it_n * gridDim.x + blockIdx.x, 0);
+
+            for (int j = (g0 & 1) == grp ? 0 : 1; j < it.n_kv; j += 2) {
+                const int g = g0 + j;                     // global tile index; g & 1 == grp
+                const int kv_start = j * kBN;
+                // The votes keep the warp together: every lane leaves the loop or none does.
+                if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&bar_sf[grp]), (g >> 1) & 1, ctl, kBarSFull))) { ok = false; break; }
+                tc_fence_after();
+                if ((tid & 127) == 0 && r == 0) FA_TS(grp * 2, j, 0);
+                uint32_t s[128];
+                tmem_ld128_wait(t_s, s);
+                tc_fence_before();                        // S is in registers: release the TMEM buffer
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&bar_sfree[grp]));
+                if ((tid & 127) == 0 && r == 0) FA_TS(grp * 2, j, 1);
+                if ((tile_min_limit - kv_start) < kBN) { // tile touches the mask or the ragged end
+                    const int limit = row_limit - kv_start;   // columns [0,limit) are visible
+#pragma unroll
+                    for (int i = 0; i < 128; i++) s[i] = (i < limit) ? s[i] : 0xff800000u;   // -inf
+                }
+                // ---- row maximum of the raw scores
+                float a0 = -INFINITY, a1 = -INFINITY, a2 = -INFINITY, a3 = -INFINITY;
+#pragma unroll
+                for (int i = 0; i < 128; i += 8) {
+                    a0 = max3(a0, __uint_as_float(s[i]), __uint_as_float(s[i + 1]));
+                    a1 = max3(a1, __uint_as_float(s[i + 2]), __uint_as_float(s[i + 3]));
+                    a2 = max3(a2, __uint_as_float(s[i + 4]), __uint_as_float(s[i + 5]));
+                    a3 = max3(a3, __uint_as_float(s[i + 6]), __uint_as_float(s[i + 7]));
+                }
+                const float tile_max = fmaxf(max3(a0, a1, a2), a3) * scale_log2;
+                // ---- the max in use: taken over from the previous tile (owned by the other group)
+                // unless this tile's max exceeds it by more than the threshold
+                float m_new = tile_max, m_prev_keep = tile_max;
+                bool changed = false;
+                if (j > 0) {
+                    if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&bar_m[grp ^ 1]), ((g - 1) >> 1) & 1, ctl, kBarM))) { ok = false; break; }
+                    const float m_prev = m_sh[r_in_tile];
+                    m_prev_keep = m_prev;
+                    changed = tile_max > m_prev + kRescaleThreshold;
+                    m_new = changed ? tile_max : m_prev;
+                }
+                m_sh[r_in_tile] = m_new;
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&bar_m[grp]));
+                if (m_new != m_mine) {                    // bring this thread's partial sum to the new reference
+                    const float f = ex2_approx(m_mine - m_new);
+                    lsum2 = fma2(lsum2, pack2(f, f), pack2(0.0f, 0.0f));
+                }
+                if ((tid & 127) == 0 && r == 0) FA_TS(grp * 2, j, 2);
+
+                // ---- rare: the max in use grew -> rescale O in TMEM before this tile's P V
+                if (__any_sync(0xffffffffu, changed)) {
+                    // P V(g-1) must have finished accumulating into O
+                    if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&bar_pv[grp ^ 1]), ((g - 1) >> 1) & 1, ctl, kBarPV))) { ok = false; break; }
+                    tc_fence_after();
+                    // rows whose max did not change multiply by one; m_mine is not the previous max of
+                    // the ROW (the other thread may have moved it), so the factor comes from m_prev
+                    const float factor = changed ? ex2_approx(m_prev_keep - m_new) : 1.0f;
+#pragma unroll 1
+                    for (int c = 0; c < D / 32; c++) {
+                        uint32_t t[32];
+                        tmem_ld32_wait(t_o + c * 32, t);
+#pragma unroll
+                        for (int i = 0; i < 32; i++) t[i] = __float_as_uint(__uint_as_float(t[i]) * factor);
+                        tmem_st_x32(t_o + c * 32, t);
+                    }
+                    tmem_wait_st();
+                }
+                m_mine = m_new;
+
+                // this group's P buffer was last read by P V(g-2), long finished by now
+                if (g >= 2) {
+                    if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&bar_pv[grp]), ((g >> 1) - 1) & 1, ctl, kBarPV))) { ok = false; break; }
+                    tc_fence_after();
+                }
+                // ---- p = 2^(s*scale*log2e - m); row sum; P -> TMEM as packed 16-bit pairs, 32 columns at a time
+                const uint64_t negm2 = pack2(-m_new, -m_new);
+#pragma unroll
+                for (int c = 0; c < 4; c++) {
+                    uint32_t pk[16];
+#pragma unroll
+                    for (int i = 0; i < 16; i++) {
+                        const int e = c * 32 + 2 * i;
+                        const uint64_t t = fma2(pack2(__uint_as_float(s[e]), __uint_as_float(s[e + 1])), scale2, negm2);
+                        float t0, t1;
+                        unpack2(t, t0, t1);
+                        const float p0 = ex2_approx(t0), p1 = ex2_approx(t1);
+                        lsum2 = add2(lsum2, pack2(p0, p1));
+                        pk[i] = pack_16<P_BF16>(p0, p1);
+                    }
+                    tmem_st_x16(t_p + c * 16, pk);
+                }
+                if ((tid & 127) == 0 && r == 0) FA_TS(grp * 2, j, 3);
+                tmem_wait_st();
                 tc_fence_before();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(smem_u32(&bar_sfree));
+                if (lane == 0) mbar_arrive(smem_u32(&bar_pf[grp]));
+                if ((tid & 127) == 0 && r == 0) FA_TS(grp * 2, j, 4);
             }
-            if ((tile_min_limit - kv_start) < BN) {      // tile touches the mask or the ragged end
-                const int limit = row_limit - kv_start;  // columns [0,limit) are visible
-#pragma unroll
-                for (int i = 0; i < 128; i++) s[i] = (i < limit) ? s[i] : 0xff800000u;   // -inf
-            }
-            // ---- row maximum of the raw scores
-            float a0 = -INFINITY, a1 = -INFINITY, a2 = -INFINITY, a3 = -INFINITY;
-#pragma unroll
-            for (int i = 0; i < 128; i += 8) {
-                a0 = max3(a0, __uint_as_float(s[i]), __uint_as_float(s[i + 1]));
-                a1 = max3(a1, __uint_as_float(s[i + 2]), __uint_as_float(s[i + 3]));
-                a2 = max3(a2, __uint_as_float(s[i + 4]), __uint_as_float(s[i + 5]));
-                a3 = max3(a3, __uint_as_float(s[i + 6]), __uint_as_float(s[i + 7]));
-            }
-            const float tile_max = fmaxf(max3(a0, a1, a2), a3) * scale_log2;
-            if (tid == 0) FA_TS(0, j, 2);
-            bool need = false;
-            if (j == 0) m_used = tile_max;
-            else need = tile_max > m_used + kRescaleThreshold;
+            if (!ok) break;
 
-            // ---- rare: the running max grew by more than the threshold -> rescale O in TMEM.
-            // O(j-1) must be complete first.  D = 128: S(j) complete implies P V(j-1) complete
-            // (the tensor pipe runs in order); D = 64: Q K^T(j) was issued ahead of P V(j-1),
-            // so wait for its commit.
-            bool pv_prev_done = !(EARLY_QK && j > 0);
-            if (__any_sync(0xffffffffu, need)) {
-                if (!pv_prev_done) {
-                    if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&bar_o), (j - 1) & 1, ctl, kBarOFull))) { ok = false; break; }
-                    tc_fence_after();
-                    pv_prev_done = true;
-                }
-                float factor = 1.0f;
-                if (need) {
-                    factor = ex2_approx(m_used - tile_max);
-                    m_used = tile_max;
-                    lsum2 = fma2(lsum2, pack2(factor, factor), pack2(0.0f, 0.0f));
-                }
-#pragma unroll 1
-                for (int c = 0; c < D / 32; c++) {
-                    uint32_t t[32];
-                    tmem_ld32_wait(t_o + c * 32, t);
-#pragma unroll
-                    for (int i = 0; i < 32; i++) t[i] = __float_as_uint(__uint_as_float(t[i]) * factor);
-                    tmem_st_x32(t_o + c * 32, t);
-                }
-                tmem_wait_st();
-            }
-
-            if (tid == 0) FA_TS(0, j, 3);
-            // ---- p = 2^(s*scale*log2e - m); row sum; P as packed 16-bit pairs, kept in
-            // registers (they replace the scores two for one) until the P columns are free.
-            const uint64_t negm2 = pack2(-m_used, -m_used);
-            uint32_t pk[64];
-#pragma unroll
-            for (int i = 0; i < 64; i++) {
-                const uint64_t t = fma2(pack2(__uint_as_float(s[2 * i]), __uint_as_float(s[2 * i + 1])), scale2, negm2);
-                float t0, t1;
-                unpack2(t, t0, t1);
-                const float p0 = ex2_approx(t0), p1 = ex2_approx(t1);
-                lsum2 = add2(lsum2, pack2(p0, p1));
-                pk[i] = pack_16<P_BF16>(p0, p1);
-            }
-            if (!pv_prev_done) {
-                // P(j-1) must have been consumed by P V(j-1) before it is overwritten; by now it
-                // normally has been, so this wait rarely blocks.
-                if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&bar_o), (j - 1) & 1, ctl, kBarOFull))) { ok = false; break; }
-                tc_fence_after();
-            }
-#pragma unroll
-            for (int c = 0; c < 4; c++) {
-                uint32_t (&chunk)[16] = *reinterpret_cast<uint32_t (*)[16]>(&pk[c * 16]);
-                tmem_st_x16(t_p + c * 16, chunk);
-            }
-            if (tid == 0) FA_TS(0, j, 4);
-            tmem_wait_st();
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(&bar_p));
-            if (tid == 0) FA_TS(0, j, 5);
-        }
-
-        if (tid == 0) FA_CTS(3);
-        // ---- epilogue: O / l -> 16-bit -> swizzled staging (the Q buffer) -> TMA store
-        ok = __all_sync(0xffffffffu, ok && mbar_wait(smem_u32(&bar_o), (n_kv - 1) & 1, ctl, kBarOFull));
-        tc_fence_after();
-        if (ok) {
+            // ---- epilogue of the item: O / l -> 16-bit -> swizzled staging -> TMA store.
+            // Both threads of a row publish (reference max, partial sum); group g converts columns
+            // [g*D/2, (g+1)*D/2) of the row.
+            if (tid == 0) FA_CTS(it_n * gridDim.x + blockIdx.x, 1);
             float l0, l1;
             unpack2(lsum2, l0, l1);
-            const float l_run = l0 + l1;
+            xm[grp][r_in_tile] = m_mine;
+            xsum[grp][r_in_tile] = l0 + l1;
+            // (a barrier of its own, one phase per item: each group waits on the other group's
+            // bar_pv only now and then, too rarely for a parity wait to be unambiguous)
+            if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&bar_odone), it_n & 1, ctl, kBarODone))) { ok = false; break; }
+            tc_fence_after();
+            uint32_t o[DH];
+            if constexpr (DH == 64) tmem_ld64_wait(t_o + grp * DH, o);
+            else tmem_ld32_wait(t_o + grp * DH, o);
+            tc_fence_before();                            // O is in registers: the next item may overwrite it
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&bar_ofree));
+            // the staging buffer must have been drained by the previous item's TMA store
+            if (tid == 0) tma_store_wait_read();
+            if (!rendezvous(smem_u32(&bar_epi), 0, kBarEpi)) { ok = false; break; }
+            const float m_a = xm[0][r_in_tile], m_b = xm[1][r_in_tile];
+            const float m_fin = fmaxf(m_a, m_b);
+            const float l_run = xsum[0][r_in_tile] * ex2_approx(m_a - m_fin) + xsum[1][r_in_tile] * ex2_approx(m_b - m_fin);
             const float inv_l = out_scale / l_run;
-#pragma unroll 1
-            for (int c = 0; c < D / 32; c++) {
-                uint32_t t[32];
-                tmem_ld32_wait(t_o + c * 32, t);
 #pragma unroll
-                for (int g4 = 0; g4 < 4; g4++) {
-                    uint32_t w[4];
+            for (int g8 = 0; g8 < DH / 8; g8++) {
+                uint32_t w[4];
 #pragma unroll
-                    for (int e = 0; e < 4; e++)
-                        w[e] = pack_16<BF16>(__uint_as_float(t[g4 * 8 + 2 * e]) * inv_l,
-                                             __uint_as_float(t[g4 * 8 + 2 * e + 1]) * inv_l);
-                    const int g = c * 4 + g4;             // 8-element (16-byte) group index in the row
-                    const uint32_t addr = o_stage + (g >> 3) * L::kQBoxBytes + r_in_tile * 128 +
-                                          (((g & 7) ^ (r_in_tile & 7)) << 4);
-                    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w[0]),
-                                 "r"(w[1]), "r"(w[2]), "r"(w[3])
-                                 : "memory");
-                }
+                for (int e = 0; e < 4; e++)
+                    w[e] = pack_16<BF16>(__uint_as_float(o[g8 * 8 + 2 * e]) * inv_l,
+                                         __uint_as_float(o[g8 * 8 + 2 * e + 1]) * inv_l);
+                const int c16 = grp * (DH / 8) + g8;      // 8-element (16-byte) group index in the row
+                const uint32_t addr = o_s + (c16 >> 3) * L::kBox + r_in_tile * 128 +
+                                      (((c16 & 7) ^ (r_in_tile & 7)) << 4);
+                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w[0]), "r"(w[1]),
+                             "r"(w[2]), "r"(w[3]) : "memory");
             }
-            if (lse_out != nullptr && row < seq_len)
-                lse_out[static_cast<size_t>(bh) * seq_len + row] = kLn2 * (m_used + log2f(l_run));
+            if (grp == 0 && lse_out != nullptr && row < seq_len)
+                lse_out[static_cast<size_t>(it.bh) * seq_len + row] = kLn2 * (m_fin + log2f(l_run));
+            fence_proxy_async_smem();
+            if (!rendezvous(smem_u32(&bar_epi), 1, kBarEpi)) { ok = false; break; }
+            if (tid == 0) {
+                for (int bx = 0; bx < NBOX; bx++)
+                    tma_store_3d(&tm_o, o_s + bx * L::kBox, bx * 64, it.q_start, it.bh);
+                tma_store_commit();
+                FA_CTS(it_n * gridDim.x + blockIdx.x, 2);
+            }
+            g0 += it.n_kv;
+            it_n++;
         }
-        fence_proxy_async_smem();
-        named_barrier_sync(1, 128);
-        if (ok && tid == 0) {
-            for (int b = 0; b < NBOX; b++)
-                tma_store_3d(&tm_o, o_stage + b * L::kQBoxBytes, b * 64, q_start, bh);
-            tma_store_commit();
-            tma_store_wait_read();        // the CTA may exit once the staging buffer has been read
-        }
-        if (tid == 0) FA_CTS(4);
+        if (tid == 0) tma_store_wait_read();              // the CTA may exit once staging has been read
     }
 
     tc_fence_before();
     __syncthreads();
-    if (warp == 5) tmem_dealloc(tmem, TMEM_COLS);
+    if (warp == 9) tmem_dealloc(tmem, TMEM_COLS);
 }
 
-template <int D, int BN, int NK, int NV, bool CAUSAL, bool BF16, bool FP8 = false>
+template <int D, bool CAUSAL, bool BF16, bool FP8>
 int launch_instance(const fa_prefill_args& a, DeviceState* st, const CUtensorMap& tq,
                     const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& to) {
-    using L = PrefillSmem<D, BN, NK, NV, FP8>;
-    auto kernel = prefill_kernel<D, BN, NK, NV, CAUSAL, BF16, FP8>;
+    using L = PrefillSmem<D, FP8>;
+    auto kernel = prefill_kernel<D, CAUSAL, BF16, FP8>;
     static bool configured[64] = {};
     if (!configured[st->device]) {
         FA_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
@@ -482,11 +597,12 @@ int launch_instance(const fa_prefill_args& a, DeviceState* st, const CUtensorMap
     }
     const int n_bh = a.batch_size * a.num_heads;
     const int n_qtiles = (a.seq_len + kBM - 1) / kBM;
-    const long long n_cta = (long long)n_bh * n_qtiles;
-    if (n_cta > 0x7FFFFFFFll) return FA_ERR_INVALID_ARGUMENT;
-    kernel<<<(unsigned)n_cta, kThreads, L::kTotal, static_cast<cudaStream_t>(a.stream)>>>(
-        tq, tk, tv, to, a.lse, a.seq_len, n_bh, n_qtiles, a.scale * kLog2e, a.q_scale, a.k_scale,
-        a.v_scale, st->status);
+    const long long n_items = (long long)n_bh * n_qtiles;
+    if (n_items > 0x7FFFFFFFll) return FA_ERR_INVALID_ARGUMENT;
+    const unsigned grid = (unsigned)(n_items < st->sm_count ? n_items : st->sm_count);
+    kernel<<<grid, kThreads, L::kTotal, static_cast<cudaStream_t>(a.stream)>>>(
+        tq, tk, tv, to, a.lse, a.seq_len, n_bh, n_qtiles, (int)n_items, a.scale * kLog2e, a.q_scale,
+        a.k_scale, a.v_scale, st->status);
     FA_CUDA_TRY(cudaGetLastError());
     return FA_OK;
 }
@@ -495,28 +611,27 @@ int launch_instance(const fa_prefill_args& a, DeviceState* st, const CUtensorMap
 
 int launch_prefill_16bit(const fa_prefill_args& a, DeviceState* st) {
     const uint64_t n_bh = (uint64_t)a.batch_size * a.num_heads;
-    constexpr int BN = 128;
     CUtensorMap tq, tk, tv, to;
     int rc;
     if ((rc = make_tensor_map_3d(&tq, a.q, a.dtype, a.d_head, a.seq_len, n_bh, 64, kBM)) != FA_OK) return rc;
-    if ((rc = make_tensor_map_3d(&tk, a.k, a.dtype, a.d_head, a.seq_len, n_bh, 64, BN)) != FA_OK) return rc;
-    if ((rc = make_tensor_map_3d(&tv, a.v, a.dtype, a.d_head, a.seq_len, n_bh, 64, BN)) != FA_OK) return rc;
+    if ((rc = make_tensor_map_3d(&tk, a.k, a.dtype, a.d_head, a.seq_len, n_bh, 64, kBN)) != FA_OK) return rc;
+    if ((rc = make_tensor_map_3d(&tv, a.v, a.dtype, a.d_head, a.seq_len, n_bh, 64, kBN)) != FA_OK) return rc;
     if ((rc = make_tensor_map_3d(&to, a.o, a.dtype, a.d_head, a.seq_len, n_bh, 64, kBM)) != FA_OK) return rc;
     const bool bf = a.dtype == FA_DTYPE_BF16;
     const bool causal = a.causal != 0;
-#define FA_DISPATCH(DH, NKS, NVS)                                                              \
-    (causal ? (bf ? launch_instance<DH, BN, NKS, NVS, true, true>(a, st, tq, tk, tv, to)       \
-                  : launch_instance<DH, BN, NKS, NVS, true, false>(a, st, tq, tk, tv, to))     \
-            : (bf ? launch_instance<DH, BN, NKS, NVS, false, true>(a, st, tq, tk, tv, to)      \
-                  : launch_instance<DH, BN, NKS, NVS, false, false>(a, st, tq, tk, tv, to)))
-    if (a.d_head == 64) return FA_DISPATCH(64, 2, 2);
-    return FA_DISPATCH(128, 1, 1);
+#define FA_DISPATCH(DH)                                                                      \
+    (causal ? (bf ? launch_instance<DH, true, true, false>(a, st, tq, tk, tv, to)            \
+                  : launch_instance<DH, true, false, false>(a, st, tq, tk, tv, to))          \
+            : (bf ? launch_instance<DH, false, true, false>(a, st, tq, tk, tv, to)           \
+                  : launch_instance<DH, false, false, false>(a, st, tq, tk, tv, to)))
+    if (a.d_head == 64) return FA_DISPATCH(64);
+    return FA_DISPATCH(128);
 #undef FA_DISPATCH
 }
 
 #ifdef FA_PHASE_TIMING
 extern "C" __attribute__((visibility("default"))) int fa_debug_phase_ts(long long* out) {
-    return (int)cudaMemcpyFromSymbol(out, g_phase_ts, sizeof(long long) * 2 * 64 * 8);
+    return (int)cudaMemcpyFromSymbol(out, g_phase_ts, sizeof(long long) * 3 * 64 * 8);
 }
 extern "C" __attribute__((visibility("default"))) int fa_debug_cta_ts(long long* out) {
     return (int)cudaMemcpyFromSymbol(out, g_cta_ts, sizeof(long long) * 4096 * 8);
@@ -526,15 +641,14 @@ extern "C" __attribute__((visibility("default"))) int fa_debug_cta_ts(long long*
 // e4m3 inputs (d_head 128), bf16 output.
 int launch_prefill_fp8(const fa_prefill_args& a, DeviceState* st) {
     const uint64_t n_bh = (uint64_t)a.batch_size * a.num_heads;
-    constexpr int BN = 128;
     CUtensorMap tq, tk, tv, to;
     int rc;
     if ((rc = make_tensor_map_3d(&tq, a.q, FA_DTYPE_E4M3, 128, a.seq_len, n_bh, 128, kBM)) != FA_OK) return rc;
-    if ((rc = make_tensor_map_3d(&tk, a.k, FA_DTYPE_E4M3, 128, a.seq_len, n_bh, 128, BN)) != FA_OK) return rc;
-    if ((rc = make_tensor_map_3d(&tv, a.v, FA_DTYPE_E4M3, 128, a.seq_len, n_bh, 128, BN)) != FA_OK) return rc;
+    if ((rc = make_tensor_map_3d(&tk, a.k, FA_DTYPE_E4M3, 128, a.seq_len, n_bh, 128, kBN)) != FA_OK) return rc;
+    if ((rc = make_tensor_map_3d(&tv, a.v, FA_DTYPE_E4M3, 128, a.seq_len, n_bh, 128, kBN)) != FA_OK) return rc;
     if ((rc = make_tensor_map_3d(&to, a.o, FA_DTYPE_BF16, 128, a.seq_len, n_bh, 64, kBM)) != FA_OK) return rc;
-    if (a.causal) return launch_instance<128, BN, 2, 1, true, true, true>(a, st, tq, tk, tv, to);
-    return launch_instance<128, BN, 2, 1, false, true, true>(a, st, tq, tk, tv, to);
+    if (a.causal) return launch_instance<128, true, true, true>(a, st, tq, tk, tv, to);
+    return launch_instance<128, false, true, true>(a, st, tq, tk, tv, to);
 }
 
 }  // namespace fa
