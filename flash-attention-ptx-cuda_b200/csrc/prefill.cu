@@ -55,8 +55,9 @@ namespace {
 constexpr int kBM = 128;                 // query rows per work item
 constexpr int kBN = 128;                 // keys per tile
 constexpr int kThreads = 512;            // 16 warps: 0-7 softmax, 8 TMA, 9 Q K^T issuer, 10 P V issuer, 12-15 e4m3 helper
-constexpr int kRegsSoftmax = 200;        // setmaxnreg targets: 256 * 200 + 256 * 56 = 512 * 128
-constexpr int kRegsOther = 56;
+constexpr int kRegsSoftmax = 192;        // setmaxnreg targets: 256 * 192 + 128 * 64 + 128 * 64 = 512 * 128
+constexpr int kRegsOther = 64;           // warps 8-11
+constexpr int kRegsHelper = 64;          // warps 12-15
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 constexpr float kRescaleThreshold = 8.0f;   // log2 units: rescale only if max grew > 2^8
@@ -64,7 +65,7 @@ constexpr float kRescaleThreshold = 8.0f;   // log2 units: rescale only if max g
 // Barrier ids reported in the status word when a wait gives up.
 enum : int { kBarQFull = 1, kBarQEmpty = 2, kBarKFull = 3, kBarKEmpty = 4, kBarVFull = 5,
              kBarVEmpty = 6, kBarSFull = 7, kBarSFree = 8, kBarPFull = 9, kBarPV = 10,
-             kBarOFree = 11, kBarV8Full = 12, kBarV8Empty = 13, kBarM = 14, kBarEpi = 15, kBarODone = 16 };
+             kBarOFree = 11, kBarV8Full = 12, kBarV8Empty = 13, kBarM = 14, kBarEpi = 15, kBarODone = 16, kBarStats = 17, kBarStatsFree = 18 };
 
 // Packed pairs of fp32 (sm_100 has two-wide fp32 FMA/ADD on 64-bit register pairs).
 __device__ __forceinline__ uint64_t pack2(float lo, float hi) {
@@ -166,9 +167,13 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     __shared__ __align__(8) uint64_t bar_kf[NK], bar_ke[NK], bar_vf[NV], bar_ve[NV];
     __shared__ __align__(8) uint64_t bar_sf[2], bar_sfree[2], bar_pf[2], bar_pv[2];
     __shared__ __align__(8) uint64_t bar_v8f[2], bar_v8e[2];
-    __shared__ __align__(8) uint64_t bar_m[2], bar_epi;      // softmax-internal hand-offs (bounded like the rest)
-    __shared__ float m_sh[128];                           // per row: the max in use, handed tile to tile
-    __shared__ float xm[2][128], xsum[2][128];            // per group and row: final reference max, partial sum
+    __shared__ __align__(8) uint64_t bar_epi;                // rendezvous of the warps that run the epilogue
+    // per item parity and row: {max in use (float bits), index of the tile it was decided for};
+    // written with one 8-byte store by the tile's owner, polled by the owner of the next tile
+    __shared__ __align__(8) uint2 m_slot[2][128];
+    // per item parity, group and row: final reference max and partial row sum of a softmax thread
+    __shared__ float xm[2][2][128], xsum[2][2][128];
+    __shared__ __align__(8) uint64_t bar_stats[2], bar_stats_free[2];
     __shared__ uint32_t tmem_slot;
     __shared__ int abort_flag;
 
@@ -184,7 +189,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     if (tid == 0) {
         mbar_init(smem_u32(&bar_qf), 1);
         mbar_init(smem_u32(&bar_qe), 1);
-        mbar_init(smem_u32(&bar_ofree), 8);
+        mbar_init(smem_u32(&bar_ofree), FP8 ? 8 : 4);    // the warps that read O in the epilogue
         mbar_init(smem_u32(&bar_odone), 1);
         for (int i = 0; i < NK; i++) { mbar_init(smem_u32(&bar_kf[i]), 1); mbar_init(smem_u32(&bar_ke[i]), 1); }
         for (int i = 0; i < NV; i++) { mbar_init(smem_u32(&bar_vf[i]), FP8 ? 128 : 1); mbar_init(smem_u32(&bar_ve[i]), 1); }
@@ -196,11 +201,12 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             mbar_init(smem_u32(&bar_v8f[i]), 1);
             mbar_init(smem_u32(&bar_v8e[i]), 128);
         }
-        for (int i = 0; i < 2; i++) mbar_init(smem_u32(&bar_m[i]), 4);   // a group published its tile's max
-        mbar_init(smem_u32(&bar_epi), 8);
+        mbar_init(smem_u32(&bar_epi), FP8 ? 8 : 4);
+        for (int i = 0; i < 2; i++) { mbar_init(smem_u32(&bar_stats[i]), 8); mbar_init(smem_u32(&bar_stats_free[i]), 4); }
         abort_flag = 0;
         fence_mbar_init();
     }
+    if (tid < 256) m_slot[tid >> 7][tid & 127] = make_uint2(0u, 0xFFFFFFFFu);   // no tile has this index
     if (warp == 8 && lane == 0) {
         prefetch_tensormap(&tm_q); prefetch_tensormap(&tm_k);
         prefetch_tensormap(&tm_v); prefetch_tensormap(&tm_o);
@@ -213,7 +219,8 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     const uint32_t tmem = tmem_slot;
     const int n_rounds = (n_items + gridDim.x - 1) / gridDim.x;
 
-    if (warp >= 8) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsOther));
+    if (warp >= 12) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsHelper));
+    else if (warp >= 8) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsOther));
     if (warp == 8) {
         // ------------------------------------------------------------ TMA producer: Q and K
         // (K and V have a producer each: a K slot frees when its Q K^T is done, a V slot only when
@@ -387,6 +394,74 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                     mbar_arrive(smem_u32(&bar_v8e[s8]));
                 }
             }
+        } else {
+            // -------------------------------------------------------- epilogue warps (16-bit inputs)
+            // One thread per query row: combine the two softmax threads' (max, sum), read the row of
+            // O from TMEM, normalise, stage in swizzled shared memory, TMA-store.  The softmax warps
+            // are already on the next item.
+            const int r_in_tile = (warp & 3) * 32 + lane;
+            const uint32_t t_o = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16) + O_COL;
+            auto rendezvous4 = [&](uint32_t parity) -> bool {
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&bar_epi));
+                return __all_sync(0xffffffffu, mbar_wait(smem_u32(&bar_epi), parity, ctl, kBarEpi));
+            };
+            int it_n = 0;
+            bool ok = true;
+            for (int r = 0; ok && r < n_rounds; r++) {
+                Item it;
+                if (!get_item<CAUSAL>(r, n_items, n_bh, n_qtiles, seq_len, it)) continue;
+                const int par = it_n & 1;
+                if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&bar_stats[par]), (it_n >> 1) & 1, ctl, kBarStats))) break;
+                const float m_a = xm[par][0][r_in_tile], m_b = xm[par][1][r_in_tile];
+                const float m_fin = fmaxf(m_a, m_b);
+                const float l_run = xsum[par][0][r_in_tile] * ex2_approx(m_a - m_fin) +
+                                    xsum[par][1][r_in_tile] * ex2_approx(m_b - m_fin);
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&bar_stats_free[par]));
+                const float inv_l = 1.0f / l_run;
+                const int row = it.q_start + r_in_tile;
+                if (lse_out != nullptr && row < seq_len)
+                    lse_out[static_cast<size_t>(it.bh) * seq_len + row] = kLn2 * (m_fin + log2f(l_run));
+                if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&bar_odone), it_n & 1, ctl, kBarODone))) break;
+                tc_fence_after();
+                // the staging buffer must have been drained by the previous item's TMA store
+                if (tid == 384) tma_store_wait_read();
+                if (!rendezvous4(0)) break;
+#pragma unroll 1
+                for (int c = 0; c < D / 32; c++) {
+                    uint32_t o[32];
+                    tmem_ld32_wait(t_o + c * 32, o);
+                    if (c == D / 32 - 1) {                // the whole row is out of TMEM: the next item may overwrite O
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(smem_u32(&bar_ofree));
+                    }
+#pragma unroll
+                    for (int g8 = 0; g8 < 4; g8++) {
+                        uint32_t w[4];
+#pragma unroll
+                        for (int e = 0; e < 4; e++)
+                            w[e] = pack_16<BF16>(__uint_as_float(o[g8 * 8 + 2 * e]) * inv_l,
+                                                 __uint_as_float(o[g8 * 8 + 2 * e + 1]) * inv_l);
+                        const int c16 = c * 4 + g8;       // 8-element (16-byte) group index in the row
+                        const uint32_t addr = o_s + (c16 >> 3) * L::kBox + r_in_tile * 128 +
+                                              (((c16 & 7) ^ (r_in_tile & 7)) << 4);
+                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w[0]), "r"(w[1]),
+                                     "r"(w[2]), "r"(w[3]) : "memory");
+                    }
+                }
+                fence_proxy_async_smem();
+                if (!rendezvous4(1)) break;
+                if (tid == 384) {
+                    for (int bx = 0; bx < NBOX; bx++)
+                        tma_store_3d(&tm_o, o_s + bx * L::kBox, bx * 64, it.q_start, it.bh);
+                    tma_store_commit();
+                    FA_CTS(it_n * gridDim.x + blockIdx.x, 2);
+                }
+                it_n++;
+            }
+            if (tid == 384) tma_store_wait_read();        // the CTA may exit once staging has been read
         }
         __syncwarp();
     } else {
@@ -459,16 +534,29 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                 // unless this tile's max exceeds it by more than the threshold
                 float m_new = tile_max, m_prev_keep = tile_max;
                 bool changed = false;
+                const uint32_t slot = smem_u32(&m_slot[it_n & 1][r_in_tile]);
                 if (j > 0) {
-                    if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&bar_m[grp ^ 1]), ((g - 1) >> 1) & 1, ctl, kBarM))) { ok = false; break; }
-                    const float m_prev = m_sh[r_in_tile];
+                    // poll for the previous tile's entry (normally long there); bounded like every wait
+                    uint32_t mb = 0, tag = 0;
+                    bool got = false;
+                    for (uint32_t spin = 0; ; spin++) {
+                        asm volatile("ld.volatile.shared.v2.b32 {%0, %1}, [%2];" : "=r"(mb), "=r"(tag) : "r"(slot));
+                        if (tag == static_cast<uint32_t>(g - 1)) { got = true; break; }
+                        if ((spin & 0xFFu) == 0xFFu && (*ctl.abort_flag || spin > (1u << 26))) break;
+                    }
+                    if (!__all_sync(0xffffffffu, got)) {
+                        *ctl.abort_flag = 1;
+                        atomicCAS(ctl.status, 0, (kErrWaitTimeout << 16) | kBarM);
+                        ok = false;
+                        break;
+                    }
+                    const float m_prev = __uint_as_float(mb);
                     m_prev_keep = m_prev;
                     changed = tile_max > m_prev + kRescaleThreshold;
                     m_new = changed ? tile_max : m_prev;
                 }
-                m_sh[r_in_tile] = m_new;
-                __syncwarp();
-                if (lane == 0) mbar_arrive(smem_u32(&bar_m[grp]));
+                asm volatile("st.volatile.shared.v2.b32 [%0], {%1, %2};" ::"r"(slot), "r"(__float_as_uint(m_new)),
+                             "r"(static_cast<uint32_t>(g)) : "memory");
                 if (m_new != m_mine) {                    // bring this thread's partial sum to the new reference
                     const float f = ex2_approx(m_mine - m_new);
                     lsum2 = fma2(lsum2, pack2(f, f), pack2(0.0f, 0.0f));
@@ -526,58 +614,72 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             }
             if (!ok) break;
 
-            // ---- epilogue of the item: O / l -> 16-bit -> swizzled staging -> TMA store.
-            // Both threads of a row publish (reference max, partial sum); group g converts columns
-            // [g*D/2, (g+1)*D/2) of the row.
             if (tid == 0) FA_CTS(it_n * gridDim.x + blockIdx.x, 1);
-            float l0, l1;
-            unpack2(lsum2, l0, l1);
-            xm[grp][r_in_tile] = m_mine;
-            xsum[grp][r_in_tile] = l0 + l1;
-            // (a barrier of its own, one phase per item: each group waits on the other group's
-            // bar_pv only now and then, too rarely for a parity wait to be unambiguous)
-            if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&bar_odone), it_n & 1, ctl, kBarODone))) { ok = false; break; }
-            tc_fence_after();
-            uint32_t o[DH];
-            if constexpr (DH == 64) tmem_ld64_wait(t_o + grp * DH, o);
-            else tmem_ld32_wait(t_o + grp * DH, o);
-            tc_fence_before();                            // O is in registers: the next item may overwrite it
-            __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(&bar_ofree));
-            // the staging buffer must have been drained by the previous item's TMA store
-            if (tid == 0) tma_store_wait_read();
-            if (!rendezvous(smem_u32(&bar_epi), 0, kBarEpi)) { ok = false; break; }
-            const float m_a = xm[0][r_in_tile], m_b = xm[1][r_in_tile];
-            const float m_fin = fmaxf(m_a, m_b);
-            const float l_run = xsum[0][r_in_tile] * ex2_approx(m_a - m_fin) + xsum[1][r_in_tile] * ex2_approx(m_b - m_fin);
-            const float inv_l = out_scale / l_run;
-#pragma unroll
-            for (int g8 = 0; g8 < DH / 8; g8++) {
-                uint32_t w[4];
-#pragma unroll
-                for (int e = 0; e < 4; e++)
-                    w[e] = pack_16<BF16>(__uint_as_float(o[g8 * 8 + 2 * e]) * inv_l,
-                                         __uint_as_float(o[g8 * 8 + 2 * e + 1]) * inv_l);
-                const int c16 = grp * (DH / 8) + g8;      // 8-element (16-byte) group index in the row
-                const uint32_t addr = o_s + (c16 >> 3) * L::kBox + r_in_tile * 128 +
-                                      (((c16 & 7) ^ (r_in_tile & 7)) << 4);
-                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w[0]), "r"(w[1]),
-                             "r"(w[2]), "r"(w[3]) : "memory");
-            }
-            if (grp == 0 && lse_out != nullptr && row < seq_len)
-                lse_out[static_cast<size_t>(it.bh) * seq_len + row] = kLn2 * (m_fin + log2f(l_run));
-            fence_proxy_async_smem();
-            if (!rendezvous(smem_u32(&bar_epi), 1, kBarEpi)) { ok = false; break; }
-            if (tid == 0) {
-                for (int bx = 0; bx < NBOX; bx++)
-                    tma_store_3d(&tm_o, o_s + bx * L::kBox, bx * 64, it.q_start, it.bh);
-                tma_store_commit();
-                FA_CTS(it_n * gridDim.x + blockIdx.x, 2);
+            if constexpr (!FP8) {
+                // ---- end of the item: hand (reference max, partial row sum) to the epilogue warps and
+                // go straight on to the next item
+                const int par = it_n & 1;
+                if (it_n >= 2 &&
+                    !__all_sync(0xffffffffu, mbar_wait(smem_u32(&bar_stats_free[par]), ((it_n >> 1) - 1) & 1, ctl, kBarStatsFree))) { ok = false; break; }
+                float l0, l1;
+                unpack2(lsum2, l0, l1);
+                xm[par][grp][r_in_tile] = m_mine;
+                xsum[par][grp][r_in_tile] = l0 + l1;
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&bar_stats[par]));
+            } else {
+                // ---- epilogue of the item: O / l -> 16-bit -> swizzled staging -> TMA store.
+                // Both threads of a row publish (reference max, partial sum); group g converts columns
+                // [g*D/2, (g+1)*D/2) of the row.
+                    float l0, l1;
+                unpack2(lsum2, l0, l1);
+                xm[0][grp][r_in_tile] = m_mine;
+                xsum[0][grp][r_in_tile] = l0 + l1;
+                // (a barrier of its own, one phase per item: each group waits on the other group's
+                // bar_pv only now and then, too rarely for a parity wait to be unambiguous)
+                if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&bar_odone), it_n & 1, ctl, kBarODone))) { ok = false; break; }
+                tc_fence_after();
+                uint32_t o[DH];
+                if constexpr (DH == 64) tmem_ld64_wait(t_o + grp * DH, o);
+                else tmem_ld32_wait(t_o + grp * DH, o);
+                tc_fence_before();                            // O is in registers: the next item may overwrite it
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&bar_ofree));
+                // the staging buffer must have been drained by the previous item's TMA store
+                if (tid == 0) tma_store_wait_read();
+                if (!rendezvous(smem_u32(&bar_epi), 0, kBarEpi)) { ok = false; break; }
+                const float m_a = xm[0][0][r_in_tile], m_b = xm[0][1][r_in_tile];
+                const float m_fin = fmaxf(m_a, m_b);
+                const float l_run = xsum[0][0][r_in_tile] * ex2_approx(m_a - m_fin) + xsum[0][1][r_in_tile] * ex2_approx(m_b - m_fin);
+                const float inv_l = out_scale / l_run;
+    #pragma unroll
+                for (int g8 = 0; g8 < DH / 8; g8++) {
+                    uint32_t w[4];
+    #pragma unroll
+                    for (int e = 0; e < 4; e++)
+                        w[e] = pack_16<BF16>(__uint_as_float(o[g8 * 8 + 2 * e]) * inv_l,
+                                             __uint_as_float(o[g8 * 8 + 2 * e + 1]) * inv_l);
+                    const int c16 = grp * (DH / 8) + g8;      // 8-element (16-byte) group index in the row
+                    const uint32_t addr = o_s + (c16 >> 3) * L::kBox + r_in_tile * 128 +
+                                          (((c16 & 7) ^ (r_in_tile & 7)) << 4);
+                    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w[0]), "r"(w[1]),
+                                 "r"(w[2]), "r"(w[3]) : "memory");
+                }
+                if (grp == 0 && lse_out != nullptr && row < seq_len)
+                    lse_out[static_cast<size_t>(it.bh) * seq_len + row] = kLn2 * (m_fin + log2f(l_run));
+                fence_proxy_async_smem();
+                if (!rendezvous(smem_u32(&bar_epi), 1, kBarEpi)) { ok = false; break; }
+                if (tid == 0) {
+                    for (int bx = 0; bx < NBOX; bx++)
+                        tma_store_3d(&tm_o, o_s + bx * L::kBox, bx * 64, it.q_start, it.bh);
+                    tma_store_commit();
+                    FA_CTS(it_n * gridDim.x + blockIdx.x, 2);
+                }
             }
             g0 += it.n_kv;
             it_n++;
         }
-        if (tid == 0) tma_store_wait_read();              // the CTA may exit once staging has been read
+        if (FP8 && tid == 0) tma_store_wait_read();       // the CTA may exit once staging has been read
     }
 
     tc_fence_before();
