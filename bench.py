@@ -39,6 +39,13 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 L2_BYTES = 126 * 1024 * 1024
+# DRAM traffic of the prefill kernel from one ncu capture (dram__bytes_read.sum + dram__bytes_write.sum,
+# profiles/prefill_d64_causal_f16_launches_and_counters.md) on 24 heads of the workload; traffic is
+# proportional to the number of heads, so it is scaled to the heads of the run.
+PREFILL_TRAFFIC_BYTES = 18.92e6
+PREFILL_TRAFFIC_NOTE = ("ncu on 24 heads: 18.92 MB read (= Q+K+V, 18.87 MB algorithmic), 0 written back during the "
+                        "kernel (O and LSE still in L2); scaled by heads")
+DECODE_TRAFFIC_BYTES = 1.0739e9 + 3.9e6   # ncu on B=4 (128 heads): read + write per launch
 CFG = dict(B=8, H=12, S=2048, D=64)
 DEC = dict(B=32, H=32, SKV=16384, D=128, SPLITS=16)
 
@@ -371,8 +378,10 @@ def run_b200_arm(args, rank, local_rank, world):
                        "l2": f"{n_sets} rotating input sets ({n_sets * 4 * bh * S * D * 2 // 2**20} MiB) > 126 MiB L2"},
             "tflops_refconv": world * refconv_flops(bh, S, D) / (ms_per_step * 1e-3) / 1e12,
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peaks["tflops"], "unit": "TFLOP/s",
-                         "frac": achieved / peaks["tflops"], "traffic": None, "peak_source": peaks["source"],
-                         "kernel": "prefill_kernel<64,128,2,2,causal,f16>", "kernel_ms": kernel_ms},
+                         "frac": achieved / peaks["tflops"], "traffic": PREFILL_TRAFFIC_BYTES * (bh / 24.0),
+                         "peak_source": peaks["source"],
+                         "kernel": "prefill_kernel<D=64,causal,f16> (persistent, 1 CTA/SM)", "kernel_ms": kernel_ms,
+                         "traffic_note": PREFILL_TRAFFIC_NOTE},
             "e2e": {"value": e2e_val, "unit": "TFLOP/s (causal FLOP count)", "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h, "ms_per_step": e2e_s * 1e3, "steps": e2e_steps},
             "gpu_launches": args.steps,
@@ -519,7 +528,8 @@ def run_decode_bench(fa, torch, dev, stream, peaks, args):
     return {"workload": f"split-KV decode fp16 B={B} H={H} Skv={SKV} D={D}, {SPLITS} splits + combine",
             "ms_per_step": ms, "tokens_per_s": B / (ms * 1e-3), "steps": steps,
             "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                         "frac": gbs / peaks["hbm_gbs"], "traffic": None, "peak_source": peaks["source"],
+                         "frac": gbs / peaks["hbm_gbs"], "traffic": DECODE_TRAFFIC_BYTES * (bh / 128.0),
+                         "peak_source": peaks["source"],
                          "algorithmic_bytes": algo_bytes,
                          "note": "K+V (8.59 GB) exceed L2; both kernels (partial + combine) inside the timed step"}}
 

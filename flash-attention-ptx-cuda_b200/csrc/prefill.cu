@@ -61,6 +61,7 @@ constexpr int kRegsHelper = 64;          // warps 12-15
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 constexpr float kRescaleThreshold = 8.0f;   // log2 units: rescale only if max grew > 2^8
+constexpr int kPolyPhase = -1;              // pairs with (index & 3) == kPolyPhase use the polynomial 2^x; -1: none
 
 // Barrier ids reported in the status word when a wait gives up.
 enum : int { kBarQFull = 1, kBarQEmpty = 2, kBarKFull = 3, kBarKEmpty = 4, kBarVFull = 5,
@@ -91,6 +92,31 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
     asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
     return d;
 }
+// 2^x for a pair, on the FMA pipe instead of the MUFU (which is the busiest pipe of this kernel:
+// 16 ex2 per clock per SM against 128 x 128 scores per tile).  x <= ~2^8 by construction (lazy
+// rescale), clamped below at -126.  Cody-Waite: n = round(x) through the 1.5*2^23 magic add,
+// f = x - n in [-0.5, 0.5], 2^f by a degree-3 minimax polynomial (relative error 7.5e-5, far
+// below the rounding of P to 16 bits), then n is added into the exponent field.
+__device__ __forceinline__ void exp2_poly_pair(uint64_t x2, float& p0, float& p1) {
+    float x0, x1;
+    unpack2(x2, x0, x1);
+    x0 = fmaxf(x0, -126.0f);
+    x1 = fmaxf(x1, -126.0f);
+    const float kMagic = 12582912.0f;
+    const uint64_t xc = pack2(x0, x1);
+    const uint64_t t = add2(xc, pack2(kMagic, kMagic));
+    const uint64_t n = add2(t, pack2(-kMagic, -kMagic));
+    const uint64_t f = fma2(n, pack2(-1.0f, -1.0f), xc);
+    uint64_t q = fma2(pack2(0.0551716685f, 0.0551716685f), f, pack2(0.2426111251f, 0.2426111251f));
+    q = fma2(q, f, pack2(0.6932609677f, 0.6932609677f));
+    q = fma2(q, f, pack2(0.9999280572f, 0.9999280572f));
+    float q0, q1, t0, t1;
+    unpack2(q, q0, q1);
+    unpack2(t, t0, t1);
+    p0 = __uint_as_float(__float_as_uint(q0) + (__float_as_uint(t0) << 23));
+    p1 = __uint_as_float(__float_as_uint(q1) + (__float_as_uint(t1) << 23));
+}
+
 // Two e4m3 codes -> two fp16 values (exact).
 __device__ __forceinline__ uint32_t e4m3x2_to_f16x2(uint16_t v) {
     uint32_t r;
@@ -120,7 +146,7 @@ struct PrefillSmem {
     static constexpr int kV8Bytes = FP8 ? kBox : 0;       // landing buffers of the e4m3 V tiles
     static constexpr int kOBytes  = kNBox * kBox;         // epilogue staging (16-bit output tile)
     static constexpr int NK  = (D == 64) ? 4 : 2;
-    static constexpr int NV  = FP8 ? 1 : ((D == 64) ? 4 : 2);
+    static constexpr int NV  = (D == 64) ? 4 : 2;
     static constexpr int NV8 = FP8 ? 2 : 0;
     static constexpr int kTotal = kQBytes + NK * kKBytes + NV * kVBytes + NV8 * kV8Bytes + kOBytes + 1024;
 };
@@ -160,7 +186,6 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     constexpr uint32_t TMEM_COLS = 512;
     constexpr bool P_BF16 = BF16 && !FP8;                 // type of P (and of the V operand of P V)
     constexpr uint32_t FMT = P_BF16 ? kFmtBF16 : kFmtF16;
-    constexpr int DH = D / 2;                             // O columns per thread of a row pair
 
     extern __shared__ uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t bar_qf, bar_qe, bar_ofree, bar_odone;
@@ -189,7 +214,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     if (tid == 0) {
         mbar_init(smem_u32(&bar_qf), 1);
         mbar_init(smem_u32(&bar_qe), 1);
-        mbar_init(smem_u32(&bar_ofree), FP8 ? 8 : 4);    // the warps that read O in the epilogue
+        mbar_init(smem_u32(&bar_ofree), 4);              // the epilogue warps have read O
         mbar_init(smem_u32(&bar_odone), 1);
         for (int i = 0; i < NK; i++) { mbar_init(smem_u32(&bar_kf[i]), 1); mbar_init(smem_u32(&bar_ke[i]), 1); }
         for (int i = 0; i < NV; i++) { mbar_init(smem_u32(&bar_vf[i]), FP8 ? 128 : 1); mbar_init(smem_u32(&bar_ve[i]), 1); }
@@ -201,7 +226,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             mbar_init(smem_u32(&bar_v8f[i]), 1);
             mbar_init(smem_u32(&bar_v8e[i]), 128);
         }
-        mbar_init(smem_u32(&bar_epi), FP8 ? 8 : 4);
+        mbar_init(smem_u32(&bar_epi), 4);
         for (int i = 0; i < 2; i++) { mbar_init(smem_u32(&bar_stats[i]), 8); mbar_init(smem_u32(&bar_stats_free[i]), 4); }
         abort_flag = 0;
         fence_mbar_init();
@@ -359,21 +384,34 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             it_n++;
         }
     } else if (warp >= 12) {
-        if constexpr (FP8) {
-            // -------------------------------------------------------- e4m3 -> fp16 V converter
-            const int ct = tid - 384;                     // 0..127
-            int g = 0;
-            bool ok = true;
-            for (int r = 0; ok && r < n_rounds; r++) {
-                Item it;
-                if (!get_item<CAUSAL>(r, n_items, n_bh, n_qtiles, seq_len, it)) continue;
+        // ------------------------------------------------------------ helper warps 12-15
+        // Epilogue of every item, one thread per query row: combine the two softmax threads'
+        // (max, sum), read the row of O from TMEM, normalise, stage in swizzled shared memory,
+        // TMA-store; the softmax warps are already on the next item.  For e4m3 inputs the same
+        // warps first turn each V tile of the item into the fp16 operand of P V.
+        const int ct = tid - 384;                         // 0..127
+        const int r_in_tile = ct;                         // == TMEM lane: (warp & 3) * 32 + lane
+        const uint32_t t_o = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16) + O_COL;
+        auto rendezvous4 = [&](uint32_t parity) -> bool {
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&bar_epi));
+            return __all_sync(0xffffffffu, mbar_wait(smem_u32(&bar_epi), parity, ctl, kBarEpi));
+        };
+        int it_n = 0, g = 0;
+        bool ok = true;
+        for (int r = 0; ok && r < n_rounds; r++) {
+            Item it;
+            if (!get_item<CAUSAL>(r, n_items, n_bh, n_qtiles, seq_len, it)) continue;
+            if constexpr (FP8) {
+                // ---- e4m3 -> fp16 conversion of the item's V tiles (exact)
                 for (int j = 0; j < it.n_kv; j++, g++) {
-                    const int s8 = g & 1;
+                    const int s8 = g & 1, sv = g % NV;
                     bool w = mbar_wait(smem_u32(&bar_v8f[s8]), (g >> 1) & 1, ctl, kBarV8Full);
-                    // the fp16 copy of tile g-1 must have been consumed by its P V
-                    if (g >= 1) w = w && mbar_wait(smem_u32(&bar_ve[0]), (g - 1) & 1, ctl, kBarVEmpty);
+                    // the fp16 buffer must have been consumed by the P V that last read it
+                    if (g >= NV) w = w && mbar_wait(smem_u32(&bar_ve[sv]), ((g / NV) - 1) & 1, ctl, kBarVEmpty);
                     if (!__all_sync(0xffffffffu, w)) { ok = false; break; }
                     const uint32_t src_base = v8_s + s8 * L::kV8Bytes;
+                    const uint32_t dst_base = v_s + sv * L::kVBytes;
 #pragma unroll 4
                     for (int i = 0; i < (kBN * 16) / 128; i++) {
                         const int c16 = ct + i * 128;         // 8-element group: row c16/16, group-in-row c16%16
@@ -385,84 +423,69 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                         const uint32_t w1 = e4m3x2_to_f16x2(static_cast<uint16_t>(lo >> 16));
                         const uint32_t w2 = e4m3x2_to_f16x2(static_cast<uint16_t>(hi & 0xFFFFu));
                         const uint32_t w3 = e4m3x2_to_f16x2(static_cast<uint16_t>(hi >> 16));
-                        const uint32_t dst = v_s + (c8 >> 3) * L::kBox + rr * 128 + (((c8 & 7) ^ (rr & 7)) << 4);
+                        const uint32_t dst = dst_base + (c8 >> 3) * L::kBox + rr * 128 + (((c8 & 7) ^ (rr & 7)) << 4);
                         asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(w0), "r"(w1),
                                      "r"(w2), "r"(w3) : "memory");
                     }
                     fence_proxy_async_smem();             // the tensor core reads the copy through the async proxy
-                    mbar_arrive(smem_u32(&bar_vf[0]));
+                    mbar_arrive(smem_u32(&bar_vf[sv]));
                     mbar_arrive(smem_u32(&bar_v8e[s8]));
                 }
+                if (!ok) break;
             }
-        } else {
-            // -------------------------------------------------------- epilogue warps (16-bit inputs)
-            // One thread per query row: combine the two softmax threads' (max, sum), read the row of
-            // O from TMEM, normalise, stage in swizzled shared memory, TMA-store.  The softmax warps
-            // are already on the next item.
-            const int r_in_tile = (warp & 3) * 32 + lane;
-            const uint32_t t_o = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16) + O_COL;
-            auto rendezvous4 = [&](uint32_t parity) -> bool {
-                __syncwarp();
-                if (lane == 0) mbar_arrive(smem_u32(&bar_epi));
-                return __all_sync(0xffffffffu, mbar_wait(smem_u32(&bar_epi), parity, ctl, kBarEpi));
-            };
-            int it_n = 0;
-            bool ok = true;
-            for (int r = 0; ok && r < n_rounds; r++) {
-                Item it;
-                if (!get_item<CAUSAL>(r, n_items, n_bh, n_qtiles, seq_len, it)) continue;
-                const int par = it_n & 1;
-                if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&bar_stats[par]), (it_n >> 1) & 1, ctl, kBarStats))) break;
-                const float m_a = xm[par][0][r_in_tile], m_b = xm[par][1][r_in_tile];
-                const float m_fin = fmaxf(m_a, m_b);
-                const float l_run = xsum[par][0][r_in_tile] * ex2_approx(m_a - m_fin) +
-                                    xsum[par][1][r_in_tile] * ex2_approx(m_b - m_fin);
-                __syncwarp();
-                if (lane == 0) mbar_arrive(smem_u32(&bar_stats_free[par]));
-                const float inv_l = 1.0f / l_run;
-                const int row = it.q_start + r_in_tile;
-                if (lse_out != nullptr && row < seq_len)
-                    lse_out[static_cast<size_t>(it.bh) * seq_len + row] = kLn2 * (m_fin + log2f(l_run));
-                if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&bar_odone), it_n & 1, ctl, kBarODone))) break;
-                tc_fence_after();
-                // the staging buffer must have been drained by the previous item's TMA store
-                if (tid == 384) tma_store_wait_read();
-                if (!rendezvous4(0)) break;
+            // ---- epilogue of the item
+            const int par = it_n & 1;
+            if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&bar_stats[par]), (it_n >> 1) & 1, ctl, kBarStats))) break;
+            const float m_a = xm[par][0][r_in_tile], m_b = xm[par][1][r_in_tile];
+            const float m_fin = fmaxf(m_a, m_b);
+            const float l_run = xsum[par][0][r_in_tile] * ex2_approx(m_a - m_fin) +
+                                xsum[par][1][r_in_tile] * ex2_approx(m_b - m_fin);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&bar_stats_free[par]));
+            float inv_l = 1.0f / l_run;
+            if constexpr (FP8) inv_l *= v_scale[it.bh];
+            const int row = it.q_start + r_in_tile;
+            if (lse_out != nullptr && row < seq_len)
+                lse_out[static_cast<size_t>(it.bh) * seq_len + row] = kLn2 * (m_fin + log2f(l_run));
+            if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&bar_odone), it_n & 1, ctl, kBarODone))) break;
+            tc_fence_after();
+            // the staging buffer must have been drained by the previous item's TMA store
+            if (tid == 384) tma_store_wait_read();
+            if (!rendezvous4(0)) break;
 #pragma unroll 1
-                for (int c = 0; c < D / 32; c++) {
-                    uint32_t o[32];
-                    tmem_ld32_wait(t_o + c * 32, o);
-                    if (c == D / 32 - 1) {                // the whole row is out of TMEM: the next item may overwrite O
-                        tc_fence_before();
-                        __syncwarp();
-                        if (lane == 0) mbar_arrive(smem_u32(&bar_ofree));
-                    }
-#pragma unroll
-                    for (int g8 = 0; g8 < 4; g8++) {
-                        uint32_t w[4];
-#pragma unroll
-                        for (int e = 0; e < 4; e++)
-                            w[e] = pack_16<BF16>(__uint_as_float(o[g8 * 8 + 2 * e]) * inv_l,
-                                                 __uint_as_float(o[g8 * 8 + 2 * e + 1]) * inv_l);
-                        const int c16 = c * 4 + g8;       // 8-element (16-byte) group index in the row
-                        const uint32_t addr = o_s + (c16 >> 3) * L::kBox + r_in_tile * 128 +
-                                              (((c16 & 7) ^ (r_in_tile & 7)) << 4);
-                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w[0]), "r"(w[1]),
-                                     "r"(w[2]), "r"(w[3]) : "memory");
-                    }
+            for (int c = 0; c < D / 32; c++) {
+                uint32_t o[32];
+                tmem_ld32_wait(t_o + c * 32, o);
+                if (c == D / 32 - 1) {                    // the whole row is out of TMEM: the next item may overwrite O
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(smem_u32(&bar_ofree));
                 }
-                fence_proxy_async_smem();
-                if (!rendezvous4(1)) break;
-                if (tid == 384) {
-                    for (int bx = 0; bx < NBOX; bx++)
-                        tma_store_3d(&tm_o, o_s + bx * L::kBox, bx * 64, it.q_start, it.bh);
-                    tma_store_commit();
-                    FA_CTS(it_n * gridDim.x + blockIdx.x, 2);
+#pragma unroll
+                for (int g8 = 0; g8 < 4; g8++) {
+                    uint32_t w[4];
+#pragma unroll
+                    for (int e = 0; e < 4; e++)
+                        w[e] = pack_16<BF16>(__uint_as_float(o[g8 * 8 + 2 * e]) * inv_l,
+                                             __uint_as_float(o[g8 * 8 + 2 * e + 1]) * inv_l);
+                    const int c16 = c * 4 + g8;           // 8-element (16-byte) group index in the row
+                    const uint32_t addr = o_s + (c16 >> 3) * L::kBox + r_in_tile * 128 +
+                                          (((c16 & 7) ^ (r_in_tile & 7)) << 4);
+                    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w[0]), "r"(w[1]),
+                                 "r"(w[2]), "r"(w[3]) : "memory");
                 }
-                it_n++;
             }
-            if (tid == 384) tma_store_wait_read();        // the CTA may exit once staging has been read
+            fence_proxy_async_smem();
+            if (!rendezvous4(1)) break;
+            if (tid == 384) {
+                for (int bx = 0; bx < NBOX; bx++)
+                    tma_store_3d(&tm_o, o_s + bx * L::kBox, bx * 64, it.q_start, it.bh);
+                tma_store_commit();
+                FA_CTS(it_n * gridDim.x + blockIdx.x, 2);
+            }
+            it_n++;
         }
+        if (tid == 384) tma_store_wait_read();            // the CTA may exit once staging has been read
         __syncwarp();
     } else {
         // ------------------------------------------------------------ softmax + epilogue (warps 0-7)
@@ -473,13 +496,6 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         const uint32_t t_s = tmem + lane_off + grp * 128;
         const uint32_t t_p = tmem + lane_off + 384 + grp * 64;
         const uint32_t t_o = tmem + lane_off + O_COL;
-        // Rendezvous of softmax warps on an mbarrier (one arrival per warp); makes the shared-memory
-        // writes of every lane before it visible to every lane after it.
-        auto rendezvous = [&](uint32_t bar, uint32_t parity, int id) -> bool {
-            __syncwarp();
-            if (lane == 0) mbar_arrive(bar);
-            return __all_sync(0xffffffffu, mbar_wait(bar, parity, ctl, id));
-        };
         int g0 = 0, it_n = 0;
         bool ok = true;
 
@@ -489,11 +505,8 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             const int row = it.q_start + r_in_tile;
             const int row_limit = CAUSAL ? min(seq_len, row + 1) : seq_len;   // keys [0,row_limit) visible
             const int tile_min_limit = CAUSAL ? min(seq_len, it.q_start + 1) : seq_len;
-            float scale_log2 = scale_log2_in, out_scale = 1.0f;
-            if constexpr (FP8) {
-                scale_log2 *= q_scale[it.bh] * k_scale[it.bh];
-                out_scale = v_scale[it.bh];
-            }
+            float scale_log2 = scale_log2_in;
+            if constexpr (FP8) scale_log2 *= q_scale[it.bh] * k_scale[it.bh];
             const uint64_t scale2 = pack2(scale_log2, scale_log2);
             // Running state of THIS thread: the reference max its partial row sum is expressed in.
             // The row's two threads alternate tiles; the max in use travels from tile to tile
@@ -588,23 +601,42 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                     if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&bar_pv[grp]), ((g >> 1) - 1) & 1, ctl, kBarPV))) { ok = false; break; }
                     tc_fence_after();
                 }
-                // ---- p = 2^(s*scale*log2e - m); row sum; P -> TMEM as packed 16-bit pairs, 32 columns at a time
+                // ---- ping-pong: the exponentials of tile g start when those of tile g-1 (other group)
+                // are done, so one group has the MUFU pipe to itself while the other loads, reduces
+                // and stores; left to themselves the two groups drift into overlapping phases.
+                // ---- p = 2^(s*scale*log2e - m); row sum; P -> TMEM as packed 16-bit pairs
                 const uint64_t negm2 = pack2(-m_new, -m_new);
+                uint64_t acc0 = lsum2, acc1 = pack2(0.0f, 0.0f), acc2 = acc1, acc3 = acc1;   // independent sum chains
+                constexpr int NCHUNK = 4;                 // P is stored 32 columns at a time
+                constexpr int PAIRS = 64 / NCHUNK;        // 16-bit pairs (TMEM columns of P) per store
 #pragma unroll
-                for (int c = 0; c < 4; c++) {
-                    uint32_t pk[16];
+                for (int c = 0; c < NCHUNK; c++) {
+                    uint32_t pk[PAIRS];
 #pragma unroll
-                    for (int i = 0; i < 16; i++) {
-                        const int e = c * 32 + 2 * i;
+                    for (int i = 0; i < PAIRS; i++) {
+                        const int e = 2 * (c * PAIRS + i);
                         const uint64_t t = fma2(pack2(__uint_as_float(s[e]), __uint_as_float(s[e + 1])), scale2, negm2);
-                        float t0, t1;
-                        unpack2(t, t0, t1);
-                        const float p0 = ex2_approx(t0), p1 = ex2_approx(t1);
-                        lsum2 = add2(lsum2, pack2(p0, p1));
+                        float p0, p1;
+                        if ((i & 3) == kPolyPhase) {      // (compiled out unless kPolyPhase is 0..3)
+                            exp2_poly_pair(t, p0, p1);
+                        } else {
+                            float t0, t1;
+                            unpack2(t, t0, t1);
+                            p0 = ex2_approx(t0);
+                            p1 = ex2_approx(t1);
+                        }
+                        const uint64_t pp = pack2(p0, p1);
+                        if ((i & 3) == 0) acc0 = add2(acc0, pp);
+                        else if ((i & 3) == 1) acc1 = add2(acc1, pp);
+                        else if ((i & 3) == 2) acc2 = add2(acc2, pp);
+                        else acc3 = add2(acc3, pp);
                         pk[i] = pack_16<P_BF16>(p0, p1);
                     }
-                    tmem_st_x16(t_p + c * 16, pk);
+#pragma unroll
+                    for (int q = 0; q < PAIRS / 16; q++)
+                        tmem_st_x16(t_p + c * PAIRS + q * 16, *reinterpret_cast<uint32_t (*)[16]>(&pk[q * 16]));
                 }
+                lsum2 = add2(add2(acc0, acc1), add2(acc2, acc3));
                 if ((tid & 127) == 0 && r == 0) FA_TS(grp * 2, j, 3);
                 tmem_wait_st();
                 tc_fence_before();
@@ -615,7 +647,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             if (!ok) break;
 
             if (tid == 0) FA_CTS(it_n * gridDim.x + blockIdx.x, 1);
-            if constexpr (!FP8) {
+            {
                 // ---- end of the item: hand (reference max, partial row sum) to the epilogue warps and
                 // go straight on to the next item
                 const int par = it_n & 1;
@@ -627,59 +659,10 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                 xsum[par][grp][r_in_tile] = l0 + l1;
                 __syncwarp();
                 if (lane == 0) mbar_arrive(smem_u32(&bar_stats[par]));
-            } else {
-                // ---- epilogue of the item: O / l -> 16-bit -> swizzled staging -> TMA store.
-                // Both threads of a row publish (reference max, partial sum); group g converts columns
-                // [g*D/2, (g+1)*D/2) of the row.
-                    float l0, l1;
-                unpack2(lsum2, l0, l1);
-                xm[0][grp][r_in_tile] = m_mine;
-                xsum[0][grp][r_in_tile] = l0 + l1;
-                // (a barrier of its own, one phase per item: each group waits on the other group's
-                // bar_pv only now and then, too rarely for a parity wait to be unambiguous)
-                if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&bar_odone), it_n & 1, ctl, kBarODone))) { ok = false; break; }
-                tc_fence_after();
-                uint32_t o[DH];
-                if constexpr (DH == 64) tmem_ld64_wait(t_o + grp * DH, o);
-                else tmem_ld32_wait(t_o + grp * DH, o);
-                tc_fence_before();                            // O is in registers: the next item may overwrite it
-                __syncwarp();
-                if (lane == 0) mbar_arrive(smem_u32(&bar_ofree));
-                // the staging buffer must have been drained by the previous item's TMA store
-                if (tid == 0) tma_store_wait_read();
-                if (!rendezvous(smem_u32(&bar_epi), 0, kBarEpi)) { ok = false; break; }
-                const float m_a = xm[0][0][r_in_tile], m_b = xm[0][1][r_in_tile];
-                const float m_fin = fmaxf(m_a, m_b);
-                const float l_run = xsum[0][0][r_in_tile] * ex2_approx(m_a - m_fin) + xsum[0][1][r_in_tile] * ex2_approx(m_b - m_fin);
-                const float inv_l = out_scale / l_run;
-    #pragma unroll
-                for (int g8 = 0; g8 < DH / 8; g8++) {
-                    uint32_t w[4];
-    #pragma unroll
-                    for (int e = 0; e < 4; e++)
-                        w[e] = pack_16<BF16>(__uint_as_float(o[g8 * 8 + 2 * e]) * inv_l,
-                                             __uint_as_float(o[g8 * 8 + 2 * e + 1]) * inv_l);
-                    const int c16 = grp * (DH / 8) + g8;      // 8-element (16-byte) group index in the row
-                    const uint32_t addr = o_s + (c16 >> 3) * L::kBox + r_in_tile * 128 +
-                                          (((c16 & 7) ^ (r_in_tile & 7)) << 4);
-                    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w[0]), "r"(w[1]),
-                                 "r"(w[2]), "r"(w[3]) : "memory");
-                }
-                if (grp == 0 && lse_out != nullptr && row < seq_len)
-                    lse_out[static_cast<size_t>(it.bh) * seq_len + row] = kLn2 * (m_fin + log2f(l_run));
-                fence_proxy_async_smem();
-                if (!rendezvous(smem_u32(&bar_epi), 1, kBarEpi)) { ok = false; break; }
-                if (tid == 0) {
-                    for (int bx = 0; bx < NBOX; bx++)
-                        tma_store_3d(&tm_o, o_s + bx * L::kBox, bx * 64, it.q_start, it.bh);
-                    tma_store_commit();
-                    FA_CTS(it_n * gridDim.x + blockIdx.x, 2);
-                }
             }
             g0 += it.n_kv;
             it_n++;
         }
-        if (FP8 && tid == 0) tma_store_wait_read();       // the CTA may exit once staging has been read
     }
 
     tc_fence_before();
