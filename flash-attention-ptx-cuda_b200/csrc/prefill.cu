@@ -55,9 +55,14 @@ namespace {
 constexpr int kBM = 128;                 // query rows per work item
 constexpr int kBN = 128;                 // keys per tile
 constexpr int kThreads = 512;            // 16 warps: 0-7 softmax, 8 TMA, 9 Q K^T issuer, 10 P V issuer, 12-15 e4m3 helper
-constexpr int kRegsSoftmax = 192;        // setmaxnreg targets: 256 * 192 + 128 * 64 + 128 * 64 = 512 * 128
+// setmaxnreg moves registers inside the pool the CTA got at launch (threads x registers at launch,
+// not the whole register file): an increase beyond that pool blocks forever.
+constexpr int kRegsLaunch = (65536 / kThreads) / 8 * 8;   // 128 at 512 threads (what __launch_bounds__ yields)
+constexpr int kRegsSoftmax = 192;        // warps 0-7
 constexpr int kRegsOther = 64;           // warps 8-11
 constexpr int kRegsHelper = 64;          // warps 12-15
+static_assert(256 * kRegsSoftmax + 128 * kRegsOther + 128 * kRegsHelper <= kThreads * kRegsLaunch,
+              "setmaxnreg targets exceed the CTA's register pool");
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 constexpr float kRescaleThreshold = 8.0f;   // log2 units: rescale only if max grew > 2^8
