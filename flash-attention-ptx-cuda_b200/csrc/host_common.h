@@ -24,6 +24,9 @@ struct DeviceState {
     int*   status      = nullptr;   // device int, error word written by kernels
     void*  stage[8]    = {};        // host-entry staging buffers (device memory)
     size_t stage_bytes[8] = {};
+    cudaStream_t pipe[3] = {};      // host-entry streams: chunks of heads are copied in, computed
+                                    // and copied out on alternating streams so the two PCIe
+                                    // directions and the kernels overlap
 };
 
 // State of the current device (created on first use).  nullptr on CUDA failure.

@@ -80,7 +80,10 @@ int fa_prefill(const fa_prefill_args* args);
  * the call pattern of the reference's own verification and demo programs
  * (src/bench.cu:250-275, src/demo.cu:282-322: cudaMalloc, cudaMemcpy H2D,
  * launch, cudaMemcpy D2H) folded into one entry point.  Device staging
- * buffers are kept per device and grown on demand.  `stream` is ignored.
+ * buffers are kept per device and grown on demand.  Large inputs are cut into
+ * chunks of heads that flow through three internal streams, so the copies in
+ * both PCIe directions and the kernels overlap; use pinned host memory to
+ * benefit.  `stream` is ignored.
  */
 int fa_prefill_host(const fa_prefill_args* args_with_host_pointers);
 
