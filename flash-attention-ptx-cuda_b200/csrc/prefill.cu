@@ -18,31 +18,36 @@
 //   (one lane each)    tiles (128 keys) through mbarrier-guarded shared-memory rings,
 //                      128-byte swizzle.  K and V have a producer each so that K loads
 //                      are not held back behind the later-freed V slots.
-//   warp 9             issues S = Q K^T (tcgen05.mma, lane 0) into one of TWO score
-//                      buffers in TMEM; it runs up to two tiles ahead of the softmax
-//                      and only waits for a score buffer to be handed back.
-//   warp 10            issues O += P V: P from TMEM (one of two P buffers), V
-//                      (MN-major) from shared memory.  Q K^T and P V have an issuer
-//                      each because every tcgen05.mma / commit costs its issuing
-//                      thread ~50 clocks; one thread doing both was the bottleneck.
+//   warp 9             issues S = Q K^T (tcgen05.mma, lane 0) into one of THREE score
+//                      buffers in TMEM, used round-robin; it waits for the tile's K and
+//                      for the P V that last read the buffer (three tiles back).
+//   warp 10            issues O += P V: P from TMEM, V (MN-major) from shared memory.
+//                      Q K^T and P V have an issuer each because every tcgen05.mma /
+//                      commit costs its issuing thread ~50-100 clocks; one thread doing
+//                      both was the bottleneck.  Each issuer commits once per tile, onto a
+//                      ring of completion barriers that every interested party waits on
+//                      (softmax: S is there; K producer: slot free / Q K^T issuer: score
+//                      buffer free; V producer: slot free; softmax: O may be rescaled).
 //   warps 0-7          softmax, two groups of four warps.  Group 0 owns the even key
-//                      tiles (S0, P0), group 1 the odd ones (S1, P1), so the two
-//                      groups are in different phases of their tiles and keep the
-//                      MUFU pipe busy between them.  A thread owns a whole query row
-//                      (TMEM lane) of its tiles: one tcgen05.ld brings the 128 scores
-//                      into registers, no cross-thread reduction; p = 2^(s*scale*log2e
-//                      - m) with packed f32x2 arithmetic; P goes back to TMEM as
-//                      16-bit pairs.  The max in use is handed from tile to tile
-//                      through shared memory; it only moves (and O is only rescaled,
-//                      in TMEM) when a tile's max exceeds it by more than 2^8.
-//                      Epilogue per item: O / l -> 16-bit -> swizzled
-//                      staging -> TMA store (clipped per head); LSE as fp32.  The
-//                      tensor pipe already works on the next item meanwhile.
-//   warps 12-15        e4m3 only: turn each V tile into the fp16 operand of P V.
-//   (for 16-bit inputs warps 12-15 only donate registers.)
+//                      tiles, group 1 the odd ones, so the two groups are in different
+//                      phases of their tiles and share the MUFU pipe.  A thread owns a
+//                      whole query row (TMEM lane) of its tiles: one tcgen05.ld brings the
+//                      128 scores into registers, no cross-thread reduction; p =
+//                      2^(s*scale*log2e - m) with packed f32x2 arithmetic; P goes back to
+//                      TMEM as 16-bit pairs IN PLACE, over the first 64 columns of the
+//                      scores it came from, so the softmax never waits for a P buffer.
+//                      The max in use is handed from tile to tile through tagged
+//                      shared-memory slots; it only moves (and O is only rescaled, in
+//                      TMEM) when a tile's max exceeds it by more than 2^8.  At the end of
+//                      an item the two threads of a row leave (max, partial sum) for the
+//                      epilogue and go straight on to the next item.
+//   warps 12-15        epilogue of every item, one thread per query row: combine the two
+//                      partial sums, O / l -> 16-bit -> swizzled staging -> TMA store
+//                      (clipped per head); LSE as fp32.  The tensor pipe and the softmax
+//                      already work on the next item meanwhile.  For e4m3 inputs the same
+//                      warps first turn each V tile into the fp16 operand of P V.
 //
-// TMEM (all 512 columns): S0 [0,128) S1 [128,256) O [256,256+D) P0 [384,448)
-// P1 [448,512).
+// TMEM (all 512 columns): three score buffers [0,128) [128,256) [256,384), O [384,384+D).
 #include <cmath>
 
 #include "host_common.h"
@@ -54,7 +59,7 @@ namespace {
 
 constexpr int kBM = 128;                 // query rows per work item
 constexpr int kBN = 128;                 // keys per tile
-constexpr int kThreads = 512;            // 16 warps: 0-7 softmax, 8 TMA, 9 Q K^T issuer, 10 P V issuer, 12-15 e4m3 helper
+constexpr int kThreads = 512;            // 16 warps: 0-7 softmax, 8 and 11 TMA, 9 Q K^T issuer, 10 P V issuer, 12-15 epilogue (+ e4m3 V conversion)
 // setmaxnreg moves registers inside the pool the CTA got at launch (threads x registers at launch,
 // not the whole register file): an increase beyond that pool blocks forever.
 constexpr int kRegsLaunch = (65536 / kThreads) / 8 * 8;   // 128 at 512 threads (what __launch_bounds__ yields)
@@ -63,6 +68,8 @@ constexpr int kRegsOther = 64;           // warps 8-11
 constexpr int kRegsHelper = 64;          // warps 12-15
 static_assert(256 * kRegsSoftmax + 128 * kRegsOther + 128 * kRegsHelper <= kThreads * kRegsLaunch,
               "setmaxnreg targets exceed the CTA's register pool");
+constexpr int kNU = 3;                   // score buffers in TMEM (S, then P in place), used round-robin
+constexpr int kRing = 4;                 // entries of the Q K^T / P V completion rings
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 constexpr float kRescaleThreshold = 8.0f;   // log2 units: rescale only if max grew > 2^8
@@ -187,15 +194,19 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     static_assert(!FP8 || (D == 128 && BF16), "e4m3 variant: d_head 128, bf16 output");
     using L = PrefillSmem<D, FP8>;
     constexpr int NBOX = L::kNBox, NK = L::NK, NV = L::NV;
-    constexpr uint32_t O_COL = 256;
+    constexpr uint32_t O_COL = kNU * 128;
+    static_assert(NK <= kRing && NV <= kRing && kNU <= kRing, "a ring entry must not be reused before its waiters have looked");
+    static_assert(O_COL + D <= 512, "TMEM columns");
     constexpr uint32_t TMEM_COLS = 512;
     constexpr bool P_BF16 = BF16 && !FP8;                 // type of P (and of the V operand of P V)
     constexpr uint32_t FMT = P_BF16 ? kFmtBF16 : kFmtF16;
 
     extern __shared__ uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t bar_qf, bar_qe, bar_ofree, bar_odone;
-    __shared__ __align__(8) uint64_t bar_kf[NK], bar_ke[NK], bar_vf[NV], bar_ve[NV];
-    __shared__ __align__(8) uint64_t bar_sf[2], bar_sfree[2], bar_pf[2], bar_pv[2];
+    __shared__ __align__(8) uint64_t bar_kf[NK], bar_vf[NV];
+    // completion rings of the two MMA streams: Q K^T / P V of tile g arrive on entry g % kRing
+    __shared__ __align__(8) uint64_t bar_qk[kRing], bar_pvd[kRing];
+    __shared__ __align__(8) uint64_t bar_pf[kNU];            // P of the tile in score buffer u is in TMEM
     __shared__ __align__(8) uint64_t bar_v8f[2], bar_v8e[2];
     __shared__ __align__(8) uint64_t bar_epi;                // rendezvous of the warps that run the epilogue
     // per item parity and row: {max in use (float bits), index of the tile it was decided for};
@@ -221,13 +232,11 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         mbar_init(smem_u32(&bar_qe), 1);
         mbar_init(smem_u32(&bar_ofree), 4);              // the epilogue warps have read O
         mbar_init(smem_u32(&bar_odone), 1);
-        for (int i = 0; i < NK; i++) { mbar_init(smem_u32(&bar_kf[i]), 1); mbar_init(smem_u32(&bar_ke[i]), 1); }
-        for (int i = 0; i < NV; i++) { mbar_init(smem_u32(&bar_vf[i]), FP8 ? 128 : 1); mbar_init(smem_u32(&bar_ve[i]), 1); }
+        for (int i = 0; i < NK; i++) mbar_init(smem_u32(&bar_kf[i]), 1);
+        for (int i = 0; i < NV; i++) mbar_init(smem_u32(&bar_vf[i]), FP8 ? 128 : 1);
+        for (int i = 0; i < kRing; i++) { mbar_init(smem_u32(&bar_qk[i]), 1); mbar_init(smem_u32(&bar_pvd[i]), 1); }
+        for (int i = 0; i < kNU; i++) mbar_init(smem_u32(&bar_pf[i]), 4);   // one arrival per warp of the owning group
         for (int i = 0; i < 2; i++) {
-            mbar_init(smem_u32(&bar_sf[i]), 1);
-            mbar_init(smem_u32(&bar_sfree[i]), 4);       // one arrival per warp of the owning group
-            mbar_init(smem_u32(&bar_pf[i]), 4);
-            mbar_init(smem_u32(&bar_pv[i]), 1);
             mbar_init(smem_u32(&bar_v8f[i]), 1);
             mbar_init(smem_u32(&bar_v8e[i]), 128);
         }
@@ -269,7 +278,8 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                     tma_load_3d(q_s + b * L::kBox, &tm_q, smem_u32(&bar_qf), b * XSTEP, it.q_start, it.bh);
                 for (int j = 0; j < it.n_kv; j++, g++) {
                     const int sk = g % NK;
-                    if (g >= NK && !mbar_wait(smem_u32(&bar_ke[sk]), ((g / NK) - 1) & 1, ctl, kBarKEmpty)) { ok = false; break; }
+                    // the slot was last read by Q K^T of tile g - NK
+                    if (g >= NK && !mbar_wait(smem_u32(&bar_qk[(g - NK) % kRing]), ((g - NK) / kRing) & 1, ctl, kBarKEmpty)) { ok = false; break; }
                     mbar_arrive_expect_tx(smem_u32(&bar_kf[sk]), L::kKBytes);
                     for (int b = 0; b < NLOAD; b++)
                         tma_load_3d(k_s + sk * L::kKBytes + b * L::kBox, &tm_k, smem_u32(&bar_kf[sk]),
@@ -296,7 +306,8 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                         tma_load_3d(v8_s + s8 * L::kV8Bytes, &tm_v, smem_u32(&bar_v8f[s8]), 0, j * kBN, it.bh);
                     } else {
                         const int sv = g % NV;
-                        if (g >= NV && !mbar_wait(smem_u32(&bar_ve[sv]), ((g / NV) - 1) & 1, ctl, kBarVEmpty)) { ok = false; break; }
+                        // the slot was last read by P V of tile g - NV
+                        if (g >= NV && !mbar_wait(smem_u32(&bar_pvd[(g - NV) % kRing]), ((g - NV) / kRing) & 1, ctl, kBarVEmpty)) { ok = false; break; }
                         mbar_arrive_expect_tx(smem_u32(&bar_vf[sv]), L::kVBytes);
                         for (int b = 0; b < NBOX; b++)
                             tma_load_3d(v_s + sv * L::kVBytes + b * L::kBox, &tm_v, smem_u32(&bar_vf[sv]),
@@ -315,21 +326,21 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         constexpr uint32_t QKFMT = FP8 ? kFmtE4M3 : FMT;
         constexpr uint32_t idesc_qk = make_idesc(kBM, kBN, QKFMT, QKFMT, kMajorK, kMajorK);
         constexpr uint64_t hi_k = make_sdesc_hi(16, 1024);
-        int g = 0, it_n = 0;
+        int g = 0, it_n = 0, u = 0;                       // u == g % kNU: the tile's score buffer
         bool ok = true;
         for (int r = 0; ok && r < n_rounds; r++) {
             Item it;
             if (!get_item<CAUSAL>(r, n_items, n_bh, n_qtiles, seq_len, it)) continue;
             if (!mbar_wait(smem_u32(&bar_qf), it_n & 1, ctl, kBarQFull)) break;
             for (int j = 0; j < it.n_kv; j++, g++) {
-                const int b = g & 1, sk = g % NK;
+                const int sk = g % NK;
                 if (!mbar_wait(smem_u32(&bar_kf[sk]), (g / NK) & 1, ctl, kBarKFull)) { ok = false; break; }
-                // the score buffer was last used by tile g-2: the softmax warps must hold it in registers
-                if (g >= 2 && !mbar_wait(smem_u32(&bar_sfree[b]), ((g >> 1) - 1) & 1, ctl, kBarSFree)) { ok = false; break; }
+                // the score buffer last held S and then P of tile g - kNU: that P V must be done
+                if (g >= kNU && !mbar_wait(smem_u32(&bar_pvd[(g - kNU) % kRing]), ((g - kNU) / kRing) & 1, ctl, kBarSFree)) { ok = false; break; }
                 tc_fence_after();
                 if (r == 0 && lane == 0) FA_TS(1, j, 0);
                 const uint32_t kb = k_s + sk * L::kKBytes;
-                const uint32_t sc = tmem + b * 128;
+                const uint32_t sc = tmem + u * 128;
                 if constexpr (FP8) {
 #pragma unroll
                     for (int kk = 0; kk < D / 32; kk++) {         // 32 e4m3 (32 bytes) of d_head per MMA
@@ -345,12 +356,12 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                     }
                 }
                 if (lane == 0) {
-                    tc_commit(smem_u32(&bar_sf[b]));
-                    tc_commit(smem_u32(&bar_ke[sk]));
+                    tc_commit(smem_u32(&bar_qk[g % kRing]));                // S is ready; the K slot is free
                     if (j == it.n_kv - 1) tc_commit(smem_u32(&bar_qe));   // Q is dead after the item's last Q K^T
                 }
                 __syncwarp();
                 if (r == 0 && lane == 0) FA_TS(1, j, 1);
+                u = (u == kNU - 1) ? 0 : u + 1;
             }
             it_n++;
         }
@@ -358,33 +369,33 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         // ------------------------------------------------------------ P V issuer
         constexpr uint32_t idesc_pv = make_idesc(kBM, D, FMT, FMT, kMajorK, kMajorMN);
         constexpr uint64_t hi_v = make_sdesc_hi(L::kBox, 1024);
-        int g = 0, it_n = 0;
+        int g = 0, it_n = 0, u = 0, u_phase = 0;          // u == g % kNU, u_phase == (g / kNU) & 1
         bool ok = true;
         for (int r = 0; ok && r < n_rounds; r++) {
             Item it;
             if (!get_item<CAUSAL>(r, n_items, n_bh, n_qtiles, seq_len, it)) continue;
             for (int j = 0; j < it.n_kv; j++, g++) {
-                const int b = g & 1, sv = g % NV;
+                const int sv = g % NV;
                 if (!mbar_wait(smem_u32(&bar_vf[sv]), (g / NV) & 1, ctl, kBarVFull)) { ok = false; break; }
-                if (!mbar_wait(smem_u32(&bar_pf[b]), (g >> 1) & 1, ctl, kBarPFull)) { ok = false; break; }
+                if (!mbar_wait(smem_u32(&bar_pf[u]), u_phase, ctl, kBarPFull)) { ok = false; break; }
                 // the first P V of an item overwrites O: the previous item's epilogue must have read it
                 if (j == 0 && it_n > 0 && !mbar_wait(smem_u32(&bar_ofree), (it_n - 1) & 1, ctl, kBarOFree)) { ok = false; break; }
                 tc_fence_after();
                 if (r == 0 && lane == 0) FA_TS(1, j, 2);
                 const uint32_t vb = v_s + sv * L::kVBytes;
-                const uint32_t pc = tmem + 384 + b * 64;
+                const uint32_t pc = tmem + u * 128;         // P overwrote the first 64 columns of the tile's S
 #pragma unroll
                 for (int kk = 0; kk < kBN / 16; kk++) {
                     const uint64_t db = make_sdesc(vb + kk * 2048, hi_v);
                     if (lane == 0) mma_f16_ts(tmem + O_COL, pc + kk * 8, db, idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
                 }
                 if (lane == 0) {
-                    tc_commit(smem_u32(&bar_pv[b]));
-                    tc_commit(smem_u32(&bar_ve[sv]));
+                    tc_commit(smem_u32(&bar_pvd[g % kRing]));               // score buffer and V slot are free
                     if (j == it.n_kv - 1) tc_commit(smem_u32(&bar_odone));   // the item's O is complete
                 }
                 __syncwarp();
                 if (r == 0 && lane == 0) FA_TS(1, j, 3);
+                if (u == kNU - 1) { u = 0; u_phase ^= 1; } else { u++; }
             }
             it_n++;
         }
@@ -413,7 +424,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                     const int s8 = g & 1, sv = g % NV;
                     bool w = mbar_wait(smem_u32(&bar_v8f[s8]), (g >> 1) & 1, ctl, kBarV8Full);
                     // the fp16 buffer must have been consumed by the P V that last read it
-                    if (g >= NV) w = w && mbar_wait(smem_u32(&bar_ve[sv]), ((g / NV) - 1) & 1, ctl, kBarVEmpty);
+                    if (g >= NV) w = w && mbar_wait(smem_u32(&bar_pvd[(g - NV) % kRing]), ((g - NV) / kRing) & 1, ctl, kBarVEmpty);
                     if (!__all_sync(0xffffffffu, w)) { ok = false; break; }
                     const uint32_t src_base = v8_s + s8 * L::kV8Bytes;
                     const uint32_t dst_base = v_s + sv * L::kVBytes;
@@ -498,8 +509,6 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         const int grp = warp >> 2;                        // group 0 owns even tiles (S0, P0), group 1 odd ones
         const int r_in_tile = (warp & 3) * 32 + lane;     // 0..127 == TMEM lane; one thread owns the whole row
         const uint32_t lane_off = static_cast<uint32_t>((warp & 3) * 32) << 16;
-        const uint32_t t_s = tmem + lane_off + grp * 128;
-        const uint32_t t_p = tmem + lane_off + 384 + grp * 64;
         const uint32_t t_o = tmem + lane_off + O_COL;
         int g0 = 0, it_n = 0;
         bool ok = true;
@@ -515,7 +524,8 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             const uint64_t scale2 = pack2(scale_log2, scale_log2);
             // Running state of THIS thread: the reference max its partial row sum is expressed in.
             // The row's two threads alternate tiles; the max in use travels from tile to tile
-            // through m_sh, so every tile of a row is exponentiated against one agreed sequence.
+            // through the tagged m_slot entries, so every tile of a row is exponentiated against
+            // one agreed sequence.
             float m_mine = -1e30f;
             uint64_t lsum2 = pack2(0.0f, 0.0f);
             if (tid == 0) FA_CTS(it_n * gridDim.x + blockIdx.x, 0);
@@ -524,14 +534,13 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                 const int g = g0 + j;                     // global tile index; g & 1 == grp
                 const int kv_start = j * kBN;
                 // The votes keep the warp together: every lane leaves the loop or none does.
-                if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&bar_sf[grp]), (g >> 1) & 1, ctl, kBarSFull))) { ok = false; break; }
+                if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&bar_qk[g % kRing]), (g / kRing) & 1, ctl, kBarSFull))) { ok = false; break; }
                 tc_fence_after();
                 if ((tid & 127) == 0 && r == 0) FA_TS(grp * 2, j, 0);
+                const int u = g % kNU;                    // the tile's score buffer; P goes back into its first half
+                const uint32_t t_s = tmem + lane_off + u * 128;
                 uint32_t s[128];
                 tmem_ld128_wait(t_s, s);
-                tc_fence_before();                        // S is in registers: release the TMEM buffer
-                __syncwarp();
-                if (lane == 0) mbar_arrive(smem_u32(&bar_sfree[grp]));
                 if ((tid & 127) == 0 && r == 0) FA_TS(grp * 2, j, 1);
                 if ((tile_min_limit - kv_start) < kBN) { // tile touches the mask or the ragged end
                     const int limit = row_limit - kv_start;   // columns [0,limit) are visible
@@ -584,7 +593,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                 // ---- rare: the max in use grew -> rescale O in TMEM before this tile's P V
                 if (__any_sync(0xffffffffu, changed)) {
                     // P V(g-1) must have finished accumulating into O
-                    if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&bar_pv[grp ^ 1]), ((g - 1) >> 1) & 1, ctl, kBarPV))) { ok = false; break; }
+                    if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&bar_pvd[(g - 1) % kRing]), ((g - 1) / kRing) & 1, ctl, kBarPV))) { ok = false; break; }
                     tc_fence_after();
                     // rows whose max did not change multiply by one; m_mine is not the previous max of
                     // the ROW (the other thread may have moved it), so the factor comes from m_prev
@@ -601,15 +610,10 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                 }
                 m_mine = m_new;
 
-                // this group's P buffer was last read by P V(g-2), long finished by now
-                if (g >= 2) {
-                    if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&bar_pv[grp]), ((g >> 1) - 1) & 1, ctl, kBarPV))) { ok = false; break; }
-                    tc_fence_after();
-                }
-                // ---- ping-pong: the exponentials of tile g start when those of tile g-1 (other group)
-                // are done, so one group has the MUFU pipe to itself while the other loads, reduces
-                // and stores; left to themselves the two groups drift into overlapping phases.
-                // ---- p = 2^(s*scale*log2e - m); row sum; P -> TMEM as packed 16-bit pairs
+                // ---- p = 2^(s*scale*log2e - m); row sum; P -> TMEM as packed 16-bit pairs, over the
+                // first 64 columns of the scores they came from (this thread's own lane, already in
+                // registers), so the softmax never waits for a P buffer: the next tile's exponentials
+                // do not depend on this tile's P V
                 const uint64_t negm2 = pack2(-m_new, -m_new);
                 uint64_t acc0 = lsum2, acc1 = pack2(0.0f, 0.0f), acc2 = acc1, acc3 = acc1;   // independent sum chains
                 constexpr int NCHUNK = 4;                 // P is stored 32 columns at a time
@@ -639,14 +643,14 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                     }
 #pragma unroll
                     for (int q = 0; q < PAIRS / 16; q++)
-                        tmem_st_x16(t_p + c * PAIRS + q * 16, *reinterpret_cast<uint32_t (*)[16]>(&pk[q * 16]));
+                        tmem_st_x16(t_s + c * PAIRS + q * 16, *reinterpret_cast<uint32_t (*)[16]>(&pk[q * 16]));
                 }
                 lsum2 = add2(add2(acc0, acc1), add2(acc2, acc3));
                 if ((tid & 127) == 0 && r == 0) FA_TS(grp * 2, j, 3);
                 tmem_wait_st();
                 tc_fence_before();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(smem_u32(&bar_pf[grp]));
+                if (lane == 0) mbar_arrive(smem_u32(&bar_pf[u]));
                 if ((tid & 127) == 0 && r == 0) FA_TS(grp * 2, j, 4);
             }
             if (!ok) break;
