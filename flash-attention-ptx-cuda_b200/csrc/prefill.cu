@@ -73,7 +73,6 @@ constexpr int kRing = 4;                 // entries of the Q K^T / P V completio
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 constexpr float kRescaleThreshold = 8.0f;   // log2 units: rescale only if max grew > 2^8
-constexpr int kPolyPhase = -1;              // pairs with (index & 3) == kPolyPhase use the polynomial 2^x; -1: none
 
 // Barrier ids reported in the status word when a wait gives up.
 enum : int { kBarQFull = 1, kBarQEmpty = 2, kBarKFull = 3, kBarKEmpty = 4, kBarVFull = 5,
@@ -104,31 +103,6 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
     asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
     return d;
 }
-// 2^x for a pair, on the FMA pipe instead of the MUFU (which is the busiest pipe of this kernel:
-// 16 ex2 per clock per SM against 128 x 128 scores per tile).  x <= ~2^8 by construction (lazy
-// rescale), clamped below at -126.  Cody-Waite: n = round(x) through the 1.5*2^23 magic add,
-// f = x - n in [-0.5, 0.5], 2^f by a degree-3 minimax polynomial (relative error 7.5e-5, far
-// below the rounding of P to 16 bits), then n is added into the exponent field.
-__device__ __forceinline__ void exp2_poly_pair(uint64_t x2, float& p0, float& p1) {
-    float x0, x1;
-    unpack2(x2, x0, x1);
-    x0 = fmaxf(x0, -126.0f);
-    x1 = fmaxf(x1, -126.0f);
-    const float kMagic = 12582912.0f;
-    const uint64_t xc = pack2(x0, x1);
-    const uint64_t t = add2(xc, pack2(kMagic, kMagic));
-    const uint64_t n = add2(t, pack2(-kMagic, -kMagic));
-    const uint64_t f = fma2(n, pack2(-1.0f, -1.0f), xc);
-    uint64_t q = fma2(pack2(0.0551716685f, 0.0551716685f), f, pack2(0.2426111251f, 0.2426111251f));
-    q = fma2(q, f, pack2(0.6932609677f, 0.6932609677f));
-    q = fma2(q, f, pack2(0.9999280572f, 0.9999280572f));
-    float q0, q1, t0, t1;
-    unpack2(q, q0, q1);
-    unpack2(t, t0, t1);
-    p0 = __uint_as_float(__float_as_uint(q0) + (__float_as_uint(t0) << 23));
-    p1 = __uint_as_float(__float_as_uint(q1) + (__float_as_uint(t1) << 23));
-}
-
 // Two e4m3 codes -> two fp16 values (exact).
 __device__ __forceinline__ uint32_t e4m3x2_to_f16x2(uint16_t v) {
     uint32_t r;
@@ -625,15 +599,9 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                     for (int i = 0; i < PAIRS; i++) {
                         const int e = 2 * (c * PAIRS + i);
                         const uint64_t t = fma2(pack2(__uint_as_float(s[e]), __uint_as_float(s[e + 1])), scale2, negm2);
-                        float p0, p1;
-                        if ((i & 3) == kPolyPhase) {      // (compiled out unless kPolyPhase is 0..3)
-                            exp2_poly_pair(t, p0, p1);
-                        } else {
-                            float t0, t1;
-                            unpack2(t, t0, t1);
-                            p0 = ex2_approx(t0);
-                            p1 = ex2_approx(t1);
-                        }
+                        float t0, t1;
+                        unpack2(t, t0, t1);
+                        const float p0 = ex2_approx(t0), p1 = ex2_approx(t1);
                         const uint64_t pp = pack2(p0, p1);
                         if ((i & 3) == 0) acc0 = add2(acc0, pp);
                         else if ((i & 3) == 1) acc1 = add2(acc1, pp);
