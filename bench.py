@@ -486,6 +486,29 @@ def run_other_configs(fa, torch, dev, stream, peaks):
     out["e4m3_b8_h16_s4096_d128_causal"] = {"ms": ms, "tflops": tf,
                                             "frac_of_measured_bf16_peak": tf / peaks["tflops"],
                                             "note": "Q K^T on the 8-bit kind, P V on the 16-bit kind"}
+    del q8, k8, v8, o, lse
+
+    # grouped-query decode over a [B, Skv, Hkv, D] cache: the group's query heads ride in the rows of
+    # the tensor-core query tile, K and V stream once per KV head (HBM-bound: report GB/s)
+    for (b, hq, hkv, skv, d) in ((32, 32, 8, 16384, 128), (32, 32, 1, 32768, 128)):
+        kc = torch.randn((b, skv, hkv, d), device=dev, dtype=torch.float32).to(torch.float16)
+        vc = torch.randn((b, skv, hkv, d), device=dev, dtype=torch.float32).to(torch.float16)
+        qg = torch.randn((b, hq, d), device=dev, dtype=torch.float32).to(torch.float16)
+        og = torch.empty_like(qg)
+        lg = torch.empty((b, hq), device=dev, dtype=torch.float32)
+        splits = fa.decode_gqa_default_splits(b, hkv, skv)
+        wsb = fa.decode_workspace_bytes(b, hq, d, splits)
+        ws = torch.empty(wsb, device=dev, dtype=torch.uint8)
+        sc_g = float(1.0 / np.sqrt(d))
+        ms = timed(lambda: fa.decode_gqa(qg, kc, vc, og, lg, b, hq, hkv, skv, d, sc_g, dtype="f16",
+                                         kv_strides=(skv * hkv * d, d, hkv * d), workspace=ws,
+                                         workspace_bytes=wsb, stream=stream))
+        algo = 2 * b * hkv * skv * d * 2 + 2 * b * hq * d * 2
+        gbs = algo / (ms * 1e-3) / 1e9
+        out[f"gqa_decode_f16_b{b}_hq{hq}_hkv{hkv}_skv{skv}_d{d}"] = {
+            "ms": ms, "GBps": gbs, "frac_of_measured_hbm_peak": gbs / peaks["hbm_gbs"], "splits": splits,
+            "algorithmic_bytes": algo, "tokens_per_s": b / (ms * 1e-3)}
+        del kc, vc, ws
     return out
 
 

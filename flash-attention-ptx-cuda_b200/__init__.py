@@ -36,7 +36,8 @@ DTYPES = {"f16": FA_DTYPE_F16, "bf16": FA_DTYPE_BF16, "e4m3": FA_DTYPE_E4M3}
 # Every symbol include/fa_b200.h declares; the CPU-only tests check they all resolve.
 EXPORTED_SYMBOLS = (
     "fa_prefill", "fa_prefill_host", "fa_decode", "fa_decode_static", "fa_decode_workspace_bytes",
-    "fa_decode_default_splits", "fa_combine", "fa_kat", "fa_device_status",
+    "fa_decode_default_splits", "fa_decode_gqa", "fa_decode_gqa_default_splits", "fa_combine", "fa_kat",
+    "fa_device_status",
     "fa_clear_device_status", "fa_error_string", "fa_last_cuda_error", "fa_version",
 )
 
@@ -62,6 +63,21 @@ class DecodeArgs(ctypes.Structure):
         ("batch_size", ctypes.c_int), ("num_heads", ctypes.c_int), ("seq_len_kv", ctypes.c_int),
         ("d_head", ctypes.c_int), ("scale", ctypes.c_float), ("dtype", ctypes.c_int),
         ("num_splits", ctypes.c_int),
+        ("workspace", ctypes.c_void_p), ("workspace_bytes", ctypes.c_size_t),
+        ("stream", ctypes.c_void_p),
+    ]
+
+
+class DecodeGqaArgs(ctypes.Structure):
+    """Mirror of ``fa_decode_gqa_args`` (include/fa_b200.h)."""
+    _fields_ = [
+        ("q", ctypes.c_void_p), ("k", ctypes.c_void_p), ("v", ctypes.c_void_p),
+        ("o", ctypes.c_void_p), ("lse", ctypes.c_void_p),
+        ("batch_size", ctypes.c_int), ("num_q_heads", ctypes.c_int), ("num_kv_heads", ctypes.c_int),
+        ("seq_len_kv", ctypes.c_int), ("d_head", ctypes.c_int), ("scale", ctypes.c_float),
+        ("dtype", ctypes.c_int), ("num_splits", ctypes.c_int),
+        ("kv_batch_stride", ctypes.c_longlong), ("kv_head_stride", ctypes.c_longlong),
+        ("kv_row_stride", ctypes.c_longlong),
         ("workspace", ctypes.c_void_p), ("workspace_bytes", ctypes.c_size_t),
         ("stream", ctypes.c_void_p),
     ]
@@ -97,6 +113,10 @@ def lib() -> ctypes.CDLL:
         l.fa_decode_workspace_bytes.argtypes = [ctypes.c_int] * 4
         l.fa_decode_default_splits.restype = ctypes.c_int
         l.fa_decode_default_splits.argtypes = [ctypes.c_int] * 3
+        l.fa_decode_gqa.restype = ctypes.c_int
+        l.fa_decode_gqa.argtypes = [ctypes.POINTER(DecodeGqaArgs)]
+        l.fa_decode_gqa_default_splits.restype = ctypes.c_int
+        l.fa_decode_gqa_default_splits.argtypes = [ctypes.c_int] * 3
         l.fa_combine.restype = ctypes.c_int
         l.fa_combine.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_int,
                                  ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int,
@@ -190,6 +210,28 @@ def decode(*args, **kw) -> None:
     rc = decode_raw(*args, **kw)
     if rc != FA_OK:
         raise FaError(rc, "fa_decode")
+
+
+def decode_gqa_default_splits(batch_size, num_kv_heads, seq_len_kv) -> int:
+    return lib().fa_decode_gqa_default_splits(batch_size, num_kv_heads, seq_len_kv)
+
+
+def decode_gqa_raw(q, k, v, o, lse, batch_size, num_q_heads, num_kv_heads, seq_len_kv, d_head, scale,
+                   dtype="f16", num_splits=0, kv_strides=(0, 0, 0), workspace=None, workspace_bytes=0,
+                   stream=None) -> int:
+    """fa_decode_gqa; ``kv_strides`` = (batch, head, row) strides of the cache in elements
+    ((0, 0, 0) = dense [B, Hkv, Skv, D]).  Returns the status code."""
+    a = DecodeGqaArgs(_ptr(q), _ptr(k), _ptr(v), _ptr(o), _ptr(lse), batch_size, num_q_heads, num_kv_heads,
+                      seq_len_kv, d_head, scale, DTYPES[dtype] if isinstance(dtype, str) else dtype,
+                      num_splits, kv_strides[0], kv_strides[1], kv_strides[2], _ptr(workspace),
+                      workspace_bytes, _stream_handle(stream))
+    return lib().fa_decode_gqa(ctypes.byref(a))
+
+
+def decode_gqa(*args, **kw) -> None:
+    rc = decode_gqa_raw(*args, **kw)
+    if rc != FA_OK:
+        raise FaError(rc, "fa_decode_gqa")
 
 
 def combine(o_parts, lse_parts, n_parts, rows, d_head, o, lse, dtype="f16", stream=None) -> None:

@@ -80,6 +80,23 @@ int make_tensor_map_3d(CUtensorMap* out, const void* base, int dtype, uint64_t r
     return FA_OK;
 }
 
+int make_tensor_map_4d(CUtensorMap* out, const void* base, int dtype, uint64_t row_elems,
+                       uint64_t n_rows, uint64_t n_heads, uint64_t n_blocks, uint64_t row_stride,
+                       uint64_t head_stride, uint64_t block_stride, uint32_t box_cols, uint32_t box_rows) {
+    const uint64_t es = 2;
+    const CUtensorMapDataType dt = (dtype == FA_DTYPE_BF16) ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                                            : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    cuuint64_t dims[4]    = {row_elems, n_rows, n_heads, n_blocks};
+    cuuint64_t strides[3] = {row_stride * es, head_stride * es, block_stride * es};
+    cuuint32_t box[4]     = {box_cols, box_rows, 1, 1};
+    cuuint32_t estr[4]    = {1, 1, 1, 1};
+    CUresult r = g_encode(out, dt, 4, const_cast<void*>(base), dims, strides, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                          CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return note_driver_error(r, "cuTensorMapEncodeTiled");
+    return FA_OK;
+}
+
 namespace {
 
 int validate_prefill(const fa_prefill_args* a) {

@@ -405,6 +405,91 @@ FA_EXPORT int fa_decode_static(const fa_decode_args* a) {
                           (int)bh, a->d_head, a->o, a->lse, a->o_f32, a->dtype, stream);
 }
 
+// ---------------------------------------------------------------------------
+// fa_decode_gqa: grouped-query decode.  The partial pass is the prefill kernel in
+// its grouped-query mode (tcgen05: the query heads of a group are the rows of
+// the query tile); the merge over KV splits is combine_kernel.
+// ---------------------------------------------------------------------------
+namespace {
+// Number of KV splits: the persistent kernel runs ceil(items / SMs) rounds of equal items, an
+// item costs its key tiles plus about two tiles of hand-over, so take the split count with the
+// smallest rounds x (tiles per split + 2); at least 4 key tiles (512 keys) per split.  The
+// same value for every caller of the same shape.
+int gqa_splits(int sms, long long bh_kv, int seq_len_kv) {
+    const int n_tiles = (seq_len_kv + 127) / 128;
+    int cap = n_tiles / 4 > 0 ? n_tiles / 4 : 1;
+    if (cap > FA_MAX_SPLITS) cap = FA_MAX_SPLITS;
+    long long best_cost = -1;
+    int best = 1;
+    for (int s = 1; s <= cap; s++) {
+        const int tps = (n_tiles + s - 1) / s;
+        const int s_eff = (n_tiles + tps - 1) / tps;     // no empty trailing split
+        const long long rounds = (bh_kv * s_eff + sms - 1) / sms;
+        const long long cost = rounds * (tps + 2);
+        if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = s_eff; }
+    }
+    return best;
+}
+}  // namespace
+
+FA_EXPORT int fa_decode_gqa_default_splits(int batch_size, int num_kv_heads, int seq_len_kv) {
+    if (batch_size <= 0 || num_kv_heads <= 0 || seq_len_kv <= 0) return 0;
+    DeviceState* st = device_state();
+    return gqa_splits(st ? st->sm_count : 148, (long long)batch_size * num_kv_heads, seq_len_kv);
+}
+
+FA_EXPORT int fa_decode_gqa(const fa_decode_gqa_args* a) {
+    if (!a || !a->q || !a->k || !a->v || !a->o) return FA_ERR_INVALID_ARGUMENT;
+    if (a->batch_size <= 0 || a->num_q_heads <= 0 || a->num_kv_heads <= 0 || a->seq_len_kv <= 0)
+        return FA_ERR_INVALID_ARGUMENT;
+    if (a->num_q_heads % a->num_kv_heads != 0) return FA_ERR_INVALID_ARGUMENT;
+    if (!(a->scale > 0.0f) || !std::isfinite(a->scale)) return FA_ERR_INVALID_ARGUMENT;
+    if (a->dtype != FA_DTYPE_F16 && a->dtype != FA_DTYPE_BF16) return FA_ERR_UNSUPPORTED;
+    if (a->d_head != 64 && a->d_head != 128) return FA_ERR_UNSUPPORTED;
+    if (a->num_splits < 0 || a->num_splits > FA_MAX_SPLITS) return FA_ERR_UNSUPPORTED;
+    const int group = a->num_q_heads / a->num_kv_heads;
+    if (group > 128) return FA_ERR_UNSUPPORTED;
+    const long long rows = (long long)a->batch_size * a->num_q_heads;
+    if (rows > 0x7FFFFFFFll) return FA_ERR_INVALID_ARGUMENT;
+    long long rs = a->kv_row_stride, hs = a->kv_head_stride, bs = a->kv_batch_stride;
+    if (rs == 0 && hs == 0 && bs == 0) {               // dense [B, Hkv, Skv, D]
+        rs = a->d_head;
+        hs = (long long)a->seq_len_kv * a->d_head;
+        bs = hs * a->num_kv_heads;
+    }
+    if (rs < a->d_head || hs <= 0 || bs <= 0) return FA_ERR_INVALID_ARGUMENT;
+    if ((rs % 8) || (hs % 8) || (bs % 8)) return FA_ERR_MISALIGNED;
+    if (!aligned16(a->q) || !aligned16(a->k) || !aligned16(a->v) || !aligned16(a->o)) return FA_ERR_MISALIGNED;
+    DeviceState* st = device_state();
+    if (!st) return FA_ERR_CUDA;
+    if (st->cc_major != 10) return FA_ERR_NOT_SM100;
+
+    const int n_tiles = (a->seq_len_kv + 127) / 128;
+    int splits = a->num_splits ? a->num_splits
+                               : gqa_splits(st->sm_count, (long long)a->batch_size * a->num_kv_heads, a->seq_len_kv);
+    if (splits > n_tiles) splits = n_tiles;
+    const int tps = (n_tiles + splits - 1) / splits;
+    splits = (n_tiles + tps - 1) / tps;
+    const size_t need = fa_decode_workspace_bytes(a->batch_size, a->num_q_heads, a->d_head, splits);
+    if (!a->workspace || a->workspace_bytes < need || !aligned16(a->workspace)) return FA_ERR_WORKSPACE;
+    float* o_part = static_cast<float*>(a->workspace);
+    float* lse_part = reinterpret_cast<float*>(static_cast<uint8_t*>(a->workspace) +
+                                               align256((size_t)rows * splits * a->d_head * sizeof(float)));
+    cudaStream_t stream = static_cast<cudaStream_t>(a->stream);
+    GqaLaunch g{};
+    g.q = a->q; g.k = a->k; g.v = a->v;
+    g.o_part = o_part; g.lse_part = lse_part;
+    g.batch = a->batch_size; g.n_kv_heads = a->num_kv_heads; g.group = group;
+    g.kv_len = a->seq_len_kv; g.d_head = a->d_head; g.dtype = a->dtype;
+    g.n_splits = splits; g.tiles_per_split = tps;
+    g.row_stride = rs; g.head_stride = hs; g.batch_stride = bs;
+    g.scale = a->scale; g.stream = stream;
+    int rc = launch_decode_gqa(g, st);
+    if (rc != FA_OK) return rc;
+    return launch_combine(o_part, lse_part, splits, a->d_head, (long long)splits * a->d_head, 1, splits,
+                          (int)rows, a->d_head, a->o, a->lse, nullptr, a->dtype, stream);
+}
+
 FA_EXPORT int fa_combine(const float* o_parts, const float* lse_parts, int n_parts, int rows,
                          int d_head, void* o, float* lse, int dtype, void* stream) {
     if (!o_parts || !lse_parts || !o || n_parts <= 0 || rows <= 0) return FA_ERR_INVALID_ARGUMENT;

@@ -48,10 +48,30 @@ int note_driver_error(CUresult err, const char* where);
 int make_tensor_map_3d(CUtensorMap* out, const void* base, int dtype, uint64_t row_elems,
                        uint64_t n_rows, uint64_t n_heads, uint32_t box_cols, uint32_t box_rows);
 
+// Rank-4 tiled tensor map over a KV cache: dims (row_elems, n_rows, n_heads, n_blocks) with the
+// three outer strides given in ELEMENTS (each a multiple of 8); 128-byte swizzle, box
+// (box_cols, box_rows, 1, 1).  Rows past n_rows read as zero.
+int make_tensor_map_4d(CUtensorMap* out, const void* base, int dtype, uint64_t row_elems,
+                       uint64_t n_rows, uint64_t n_heads, uint64_t n_blocks, uint64_t row_stride,
+                       uint64_t head_stride, uint64_t block_stride, uint32_t box_cols, uint32_t box_rows);
+
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 // Implemented next to their kernels.
 int launch_prefill_16bit(const fa_prefill_args& a, DeviceState* st);
 int launch_prefill_fp8(const fa_prefill_args& a, DeviceState* st);
+
+// Grouped-query decode on the prefill kernel: the `group` query heads that share a KV head ride
+// in the rows of one query tile; work items are (batch x KV head, KV split).
+struct GqaLaunch {
+    const void* q; const void* k; const void* v;
+    float* o_part; float* lse_part;           // [row][split][D] and [row][split], row = b * Hq + hq
+    int batch, n_kv_heads, group, kv_len, d_head, dtype;
+    int n_splits, tiles_per_split;
+    long long row_stride, head_stride, batch_stride;   // of the KV cache, in elements
+    float scale;
+    cudaStream_t stream;
+};
+int launch_decode_gqa(const GqaLaunch& g, DeviceState* st);
 
 }  // namespace fa

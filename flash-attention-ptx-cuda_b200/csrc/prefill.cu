@@ -137,12 +137,33 @@ struct PrefillSmem {
     static constexpr int kTotal = kQBytes + NK * kKBytes + NV * kVBytes + NV8 * kV8Bytes + kOBytes + 1024;
 };
 
-// Work list: item index -> (query tile, head), heaviest first when causal.
-struct Item { int q_start, bh, n_kv; };
+// Grouped-query decode mode (device side of GqaLaunch).
+struct GqaDev {
+    float* o_part;          // [row][split][D] fp32, row = (batch x KV head) * group + query head in group
+    float* lse_part;        // [row][split]
+    int n_splits, tiles_per_split, n_tiles, group, n_hkv;
+};
 
-template <bool CAUSAL>
-__device__ __forceinline__ bool get_item(int k, int n_items, int n_bh, int n_qtiles, int seq_len, Item& it) {
+// Work list: item index -> (query tile, head), heaviest first when causal.  In grouped-query
+// decode mode an item is (batch x KV head, KV split): key tiles [t0, t0 + n_kv) of that head.
+struct Item { int q_start, bh, n_kv, t0, split; };
+
+template <bool CAUSAL, bool GQA>
+__device__ __forceinline__ bool get_item(int k, int n_items, int n_bh, int n_qtiles, int seq_len,
+                                         const GqaDev& gq, Item& it) {
     const int G = gridDim.x, c = blockIdx.x;
+    if constexpr (GQA) {
+        const int idx = k * G + c;                    // items are equal: plain round-robin
+        if (idx >= n_items) return false;
+        it.bh = idx / gq.n_splits;
+        it.split = idx - it.bh * gq.n_splits;
+        it.t0 = it.split * gq.tiles_per_split;
+        it.n_kv = min(gq.tiles_per_split, gq.n_tiles - it.t0);
+        it.q_start = 0;
+        return true;
+    }
+    it.t0 = 0;
+    it.split = 0;
     const int idx = (k & 1) ? k * G + (G - 1 - c) : k * G + c;     // boustrophedon deal
     if (idx >= n_items) return false;
     const int qt = CAUSAL ? (n_qtiles - 1 - idx / n_bh) : (idx / n_bh);
@@ -158,14 +179,16 @@ __device__ __forceinline__ bool get_item(int k, int n_items, int n_bh, int n_qti
 // 16-bit kind with P in fp16, because an e4m3 P (3 mantissa bits) misses the output tolerance.
 // The Q and K scales fold into the softmax scale, the V scale into the final normalisation;
 // the output is bf16.
-template <int D, bool CAUSAL, bool BF16, bool FP8>
+template <int D, bool CAUSAL, bool BF16, bool FP8, bool GQA>
 __global__ void __launch_bounds__(kThreads, 1)
 prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o,
                float* __restrict__ lse_out, int seq_len, int n_bh, int n_qtiles, int n_items,
                float scale_log2_in, const float* __restrict__ q_scale,
-               const float* __restrict__ k_scale, const float* __restrict__ v_scale, int* status) {
+               const float* __restrict__ k_scale, const float* __restrict__ v_scale, int* status,
+               const GqaDev gq) {
     static_assert(!FP8 || (D == 128 && BF16), "e4m3 variant: d_head 128, bf16 output");
+    static_assert(!GQA || (!CAUSAL && !FP8), "grouped-query decode: one query row per head, 16-bit inputs");
     using L = PrefillSmem<D, FP8>;
     constexpr int NBOX = L::kNBox, NK = L::NK, NV = L::NV;
     constexpr uint32_t O_COL = kNU * 128;
@@ -245,7 +268,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             bool ok = true;
             for (int r = 0; ok && r < n_rounds; r++) {
                 Item it;
-                if (!get_item<CAUSAL>(r, n_items, n_bh, n_qtiles, seq_len, it)) continue;
+                if (!get_item<CAUSAL, GQA>(r, n_items, n_bh, n_qtiles, seq_len, gq, it)) continue;
                 if (it_n > 0 && !mbar_wait(smem_u32(&bar_qe), (it_n - 1) & 1, ctl, kBarQEmpty)) break;
                 mbar_arrive_expect_tx(smem_u32(&bar_qf), L::kQBytes);
                 for (int b = 0; b < NLOAD; b++)
@@ -255,9 +278,14 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                     // the slot was last read by Q K^T of tile g - NK
                     if (g >= NK && !mbar_wait(smem_u32(&bar_qk[(g - NK) % kRing]), ((g - NK) / kRing) & 1, ctl, kBarKEmpty)) { ok = false; break; }
                     mbar_arrive_expect_tx(smem_u32(&bar_kf[sk]), L::kKBytes);
-                    for (int b = 0; b < NLOAD; b++)
-                        tma_load_3d(k_s + sk * L::kKBytes + b * L::kBox, &tm_k, smem_u32(&bar_kf[sk]),
-                                    b * XSTEP, j * kBN, it.bh);
+                    for (int b = 0; b < NLOAD; b++) {
+                        if constexpr (GQA)          // KV cache map: (d, key, KV head, batch)
+                            tma_load_4d(k_s + sk * L::kKBytes + b * L::kBox, &tm_k, smem_u32(&bar_kf[sk]),
+                                        b * XSTEP, (it.t0 + j) * kBN, it.bh % gq.n_hkv, it.bh / gq.n_hkv);
+                        else
+                            tma_load_3d(k_s + sk * L::kKBytes + b * L::kBox, &tm_k, smem_u32(&bar_kf[sk]),
+                                        b * XSTEP, j * kBN, it.bh);
+                    }
                 }
                 it_n++;
             }
@@ -270,7 +298,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             bool ok = true;
             for (int r = 0; ok && r < n_rounds; r++) {
                 Item it;
-                if (!get_item<CAUSAL>(r, n_items, n_bh, n_qtiles, seq_len, it)) continue;
+                if (!get_item<CAUSAL, GQA>(r, n_items, n_bh, n_qtiles, seq_len, gq, it)) continue;
                 for (int j = 0; j < it.n_kv; j++, g++) {
                     if constexpr (FP8) {
                         // e4m3 V lands in its own buffers; warps 12-15 turn it into the fp16 operand.
@@ -283,9 +311,14 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                         // the slot was last read by P V of tile g - NV
                         if (g >= NV && !mbar_wait(smem_u32(&bar_pvd[(g - NV) % kRing]), ((g - NV) / kRing) & 1, ctl, kBarVEmpty)) { ok = false; break; }
                         mbar_arrive_expect_tx(smem_u32(&bar_vf[sv]), L::kVBytes);
-                        for (int b = 0; b < NBOX; b++)
-                            tma_load_3d(v_s + sv * L::kVBytes + b * L::kBox, &tm_v, smem_u32(&bar_vf[sv]),
-                                        b * 64, j * kBN, it.bh);
+                        for (int b = 0; b < NBOX; b++) {
+                            if constexpr (GQA)
+                                tma_load_4d(v_s + sv * L::kVBytes + b * L::kBox, &tm_v, smem_u32(&bar_vf[sv]),
+                                            b * 64, (it.t0 + j) * kBN, it.bh % gq.n_hkv, it.bh / gq.n_hkv);
+                            else
+                                tma_load_3d(v_s + sv * L::kVBytes + b * L::kBox, &tm_v, smem_u32(&bar_vf[sv]),
+                                            b * 64, j * kBN, it.bh);
+                        }
                     }
                 }
             }
@@ -304,7 +337,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         bool ok = true;
         for (int r = 0; ok && r < n_rounds; r++) {
             Item it;
-            if (!get_item<CAUSAL>(r, n_items, n_bh, n_qtiles, seq_len, it)) continue;
+            if (!get_item<CAUSAL, GQA>(r, n_items, n_bh, n_qtiles, seq_len, gq, it)) continue;
             if (!mbar_wait(smem_u32(&bar_qf), it_n & 1, ctl, kBarQFull)) break;
             for (int j = 0; j < it.n_kv; j++, g++) {
                 const int sk = g % NK;
@@ -347,7 +380,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         bool ok = true;
         for (int r = 0; ok && r < n_rounds; r++) {
             Item it;
-            if (!get_item<CAUSAL>(r, n_items, n_bh, n_qtiles, seq_len, it)) continue;
+            if (!get_item<CAUSAL, GQA>(r, n_items, n_bh, n_qtiles, seq_len, gq, it)) continue;
             for (int j = 0; j < it.n_kv; j++, g++) {
                 const int sv = g % NV;
                 if (!mbar_wait(smem_u32(&bar_vf[sv]), (g / NV) & 1, ctl, kBarVFull)) { ok = false; break; }
@@ -391,7 +424,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         bool ok = true;
         for (int r = 0; ok && r < n_rounds; r++) {
             Item it;
-            if (!get_item<CAUSAL>(r, n_items, n_bh, n_qtiles, seq_len, it)) continue;
+            if (!get_item<CAUSAL, GQA>(r, n_items, n_bh, n_qtiles, seq_len, gq, it)) continue;
             if constexpr (FP8) {
                 // ---- e4m3 -> fp16 conversion of the item's V tiles (exact)
                 for (int j = 0; j < it.n_kv; j++, g++) {
@@ -439,6 +472,32 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                 lse_out[static_cast<size_t>(it.bh) * seq_len + row] = kLn2 * (m_fin + log2f(l_run));
             if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&bar_odone), it_n & 1, ctl, kBarODone))) break;
             tc_fence_after();
+            if constexpr (GQA) {
+                // Partial result of this KV split: normalised fp32 O and its LSE for the rows that
+                // carry a query head; the merge over splits is a separate kernel.
+                const bool live = r_in_tile < gq.group;
+                const size_t pidx = (static_cast<size_t>(it.bh) * gq.group + r_in_tile) * gq.n_splits + it.split;
+                if (live) gq.lse_part[pidx] = kLn2 * (m_fin + log2f(l_run));
+#pragma unroll 1
+                for (int c = 0; c < D / 32; c++) {
+                    uint32_t o[32];
+                    tmem_ld32_wait(t_o + c * 32, o);
+                    if (c == D / 32 - 1) {
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(smem_u32(&bar_ofree));
+                    }
+                    if (live) {
+                        float4* dst = reinterpret_cast<float4*>(gq.o_part + pidx * D + c * 32);
+#pragma unroll
+                        for (int e = 0; e < 8; e++)
+                            dst[e] = make_float4(__uint_as_float(o[4 * e]) * inv_l, __uint_as_float(o[4 * e + 1]) * inv_l,
+                                                 __uint_as_float(o[4 * e + 2]) * inv_l, __uint_as_float(o[4 * e + 3]) * inv_l);
+                    }
+                }
+                it_n++;
+                continue;
+            }
             // the staging buffer must have been drained by the previous item's TMA store
             if (tid == 384) tma_store_wait_read();
             if (!rendezvous4(0)) break;
@@ -489,7 +548,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
 
         for (int r = 0; ok && r < n_rounds; r++) {
             Item it;
-            if (!get_item<CAUSAL>(r, n_items, n_bh, n_qtiles, seq_len, it)) continue;
+            if (!get_item<CAUSAL, GQA>(r, n_items, n_bh, n_qtiles, seq_len, gq, it)) continue;
             const int row = it.q_start + r_in_tile;
             const int row_limit = CAUSAL ? min(seq_len, row + 1) : seq_len;   // keys [0,row_limit) visible
             const int tile_min_limit = CAUSAL ? min(seq_len, it.q_start + 1) : seq_len;
@@ -506,7 +565,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
 
             for (int j = (g0 & 1) == grp ? 0 : 1; j < it.n_kv; j += 2) {
                 const int g = g0 + j;                     // global tile index; g & 1 == grp
-                const int kv_start = j * kBN;
+                const int kv_start = (GQA ? it.t0 + j : j) * kBN;
                 // The votes keep the warp together: every lane leaves the loop or none does.
                 if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&bar_qk[g % kRing]), (g / kRing) & 1, ctl, kBarSFull))) { ok = false; break; }
                 tc_fence_after();
@@ -651,7 +710,7 @@ template <int D, bool CAUSAL, bool BF16, bool FP8>
 int launch_instance(const fa_prefill_args& a, DeviceState* st, const CUtensorMap& tq,
                     const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& to) {
     using L = PrefillSmem<D, FP8>;
-    auto kernel = prefill_kernel<D, CAUSAL, BF16, FP8>;
+    auto kernel = prefill_kernel<D, CAUSAL, BF16, FP8, false>;
     static bool configured[64] = {};
     if (!configured[st->device]) {
         FA_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
@@ -664,7 +723,29 @@ int launch_instance(const fa_prefill_args& a, DeviceState* st, const CUtensorMap
     const unsigned grid = (unsigned)(n_items < st->sm_count ? n_items : st->sm_count);
     kernel<<<grid, kThreads, L::kTotal, static_cast<cudaStream_t>(a.stream)>>>(
         tq, tk, tv, to, a.lse, a.seq_len, n_bh, n_qtiles, (int)n_items, a.scale * kLog2e, a.q_scale,
-        a.k_scale, a.v_scale, st->status);
+        a.k_scale, a.v_scale, st->status, GqaDev{});
+    FA_CUDA_TRY(cudaGetLastError());
+    return FA_OK;
+}
+
+template <int D, bool BF16>
+int launch_gqa_instance(const GqaLaunch& g, DeviceState* st, const CUtensorMap& tq, const CUtensorMap& tk,
+                        const CUtensorMap& tv) {
+    using L = PrefillSmem<D, false>;
+    auto kernel = prefill_kernel<D, false, BF16, false, true>;
+    static bool configured[64] = {};
+    if (!configured[st->device]) {
+        FA_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
+        configured[st->device] = true;
+    }
+    const int n_bh = g.batch * g.n_kv_heads;
+    const int n_tiles = (g.kv_len + kBN - 1) / kBN;
+    const long long n_items = (long long)n_bh * g.n_splits;
+    if (n_items > 0x7FFFFFFFll) return FA_ERR_INVALID_ARGUMENT;
+    const unsigned grid = (unsigned)(n_items < st->sm_count ? n_items : st->sm_count);
+    const GqaDev gq{g.o_part, g.lse_part, g.n_splits, g.tiles_per_split, n_tiles, g.group, g.n_kv_heads};
+    kernel<<<grid, kThreads, L::kTotal, g.stream>>>(tq, tk, tv, tq, nullptr, g.kv_len, n_bh, 1, (int)n_items,
+                                                    g.scale * kLog2e, nullptr, nullptr, nullptr, st->status, gq);
     FA_CUDA_TRY(cudaGetLastError());
     return FA_OK;
 }
@@ -689,6 +770,21 @@ int launch_prefill_16bit(const fa_prefill_args& a, DeviceState* st) {
     if (a.d_head == 64) return FA_DISPATCH(64);
     return FA_DISPATCH(128);
 #undef FA_DISPATCH
+}
+
+int launch_decode_gqa(const GqaLaunch& g, DeviceState* st) {
+    const uint64_t n_bh = (uint64_t)g.batch * g.n_kv_heads;
+    CUtensorMap tq, tk, tv;
+    int rc;
+    // Q [B, Hq, D] seen as (batch x KV head) tiles of `group` rows; rows past the group read as zero
+    if ((rc = make_tensor_map_3d(&tq, g.q, g.dtype, g.d_head, g.group, n_bh, 64, kBM)) != FA_OK) return rc;
+    if ((rc = make_tensor_map_4d(&tk, g.k, g.dtype, g.d_head, g.kv_len, g.n_kv_heads, g.batch, g.row_stride,
+                                 g.head_stride, g.batch_stride, 64, kBN)) != FA_OK) return rc;
+    if ((rc = make_tensor_map_4d(&tv, g.v, g.dtype, g.d_head, g.kv_len, g.n_kv_heads, g.batch, g.row_stride,
+                                 g.head_stride, g.batch_stride, 64, kBN)) != FA_OK) return rc;
+    const bool bf = g.dtype == FA_DTYPE_BF16;
+    if (g.d_head == 64) return bf ? launch_gqa_instance<64, true>(g, st, tq, tk, tv) : launch_gqa_instance<64, false>(g, st, tq, tk, tv);
+    return bf ? launch_gqa_instance<128, true>(g, st, tq, tk, tv) : launch_gqa_instance<128, false>(g, st, tq, tk, tv);
 }
 
 #ifdef FA_PHASE_TIMING

@@ -1,0 +1,107 @@
+"""PyTorch custom operators over the C ABI: ``torch.ops.fa_b200.prefill`` / ``decode``.
+
+Forward only (the library has no backward pass).  Tensors use the layout of
+``torch.nn.functional.scaled_dot_product_attention``: ``[B, H, S, D]``,
+contiguous, fp16 or bf16, on a CUDA device; the kernels see them as the
+reference's ``[B*H, S, D]`` (include/flash_attention.h:46-61).  The operators
+launch on the current CUDA stream of the tensors' device and allocate their
+outputs (and the decode workspace) with torch.
+
+``sdpa()`` is a convenience with the keyword names of
+``scaled_dot_product_attention`` for the cases this library covers.
+
+There is no fallback: on a machine without the library or without a B200-class
+GPU the operators raise.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+
+import fa_b200 as _fa
+from fa_b200 import FaError
+
+_DTYPES = {torch.float16: "f16", torch.bfloat16: "bf16"}
+
+
+def _check(q, k, v):
+    if q.dtype not in _DTYPES or k.dtype != q.dtype or v.dtype != q.dtype:
+        raise TypeError("fa_b200: q, k, v must share dtype float16 or bfloat16")
+    if not (q.is_cuda and k.is_cuda and v.is_cuda):
+        raise RuntimeError("fa_b200: tensors must be on a CUDA device (there is no CPU path)")
+    if q.dim() != 4 or k.dim() != 4 or v.dim() != 4:
+        raise ValueError("fa_b200: expected [B, H, S, D] tensors")
+
+
+@torch.library.custom_op("fa_b200::prefill", mutates_args=())
+def prefill(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float,
+            causal: bool) -> tuple[torch.Tensor, torch.Tensor]:
+    """Self-attention forward.  Returns (O [B,H,S,D] in the input dtype, LSE [B,H,S] fp32, natural log)."""
+    _check(q, k, v)
+    if k.shape != q.shape or v.shape != q.shape:
+        raise ValueError("fa_b200::prefill: q, k, v must have the same shape")
+    b, h, s, d = q.shape
+    q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+    o = torch.empty_like(q)
+    lse = torch.empty((b, h, s), device=q.device, dtype=torch.float32)
+    with torch.cuda.device(q.device):
+        _fa.prefill(q, k, v, o, lse, b, h, s, d, float(scale), bool(causal), dtype=_DTYPES[q.dtype],
+                    stream=torch.cuda.current_stream(q.device))
+    return o, lse
+
+
+@prefill.register_fake
+def _(q, k, v, scale, causal):
+    b, h, s, _ = q.shape
+    return torch.empty_like(q), q.new_empty((b, h, s), dtype=torch.float32)
+
+
+@torch.library.custom_op("fa_b200::decode", mutates_args=())
+def decode(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float,
+           num_splits: int) -> tuple[torch.Tensor, torch.Tensor]:
+    """One query row per head against a KV cache: q [B,H,1,D], k/v [B,H,Skv,D].
+
+    Returns (O [B,H,1,D], LSE [B,H,1]).  ``num_splits`` 0 picks the library default."""
+    _check(q, k, v)
+    b, h, one, d = q.shape
+    if one != 1 or k.shape[:2] != (b, h) or k.shape[3] != d or v.shape != k.shape:
+        raise ValueError("fa_b200::decode: expected q [B,H,1,D] and k, v [B,H,Skv,D]")
+    skv = k.shape[2]
+    q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+    o = torch.empty_like(q)
+    lse = torch.empty((b, h, 1), device=q.device, dtype=torch.float32)
+    with torch.cuda.device(q.device):
+        splits = num_splits if num_splits > 0 else _fa.decode_default_splits(b, h, skv)
+        ws_bytes = _fa.decode_workspace_bytes(b, h, d, splits)
+        ws = torch.empty(ws_bytes, device=q.device, dtype=torch.uint8)
+        _fa.decode(q, k, v, o, lse, None, b, h, skv, d, float(scale), dtype=_DTYPES[q.dtype],
+                   num_splits=splits, workspace=ws, workspace_bytes=ws_bytes,
+                   stream=torch.cuda.current_stream(q.device))
+    return o, lse
+
+
+@decode.register_fake
+def _(q, k, v, scale, num_splits):
+    b, h, _, _ = q.shape
+    return torch.empty_like(q), q.new_empty((b, h, 1), dtype=torch.float32)
+
+
+def sdpa(query: torch.Tensor, key: torch.Tensor, value: torch.Tensor, attn_mask=None,
+         dropout_p: float = 0.0, is_causal: bool = False, scale: float | None = None) -> torch.Tensor:
+    """``scaled_dot_product_attention`` for the cases the library covers (no mask, no dropout).
+
+    Self-attention (equal sequence lengths) runs the prefill kernel; a single query row against a
+    longer cache runs split-KV decode.  Anything else raises: there is no fallback."""
+    if attn_mask is not None or dropout_p != 0.0:
+        raise NotImplementedError("fa_b200.sdpa: attn_mask and dropout are not supported")
+    d = query.shape[-1]
+    sc = float(scale) if scale is not None else 1.0 / math.sqrt(d)
+    if query.shape[-2] == key.shape[-2]:
+        return prefill(query, key, value, sc, bool(is_causal))[0]
+    if query.shape[-2] == 1 and not is_causal:
+        return decode(query, key, value, sc, 0)[0]
+    raise NotImplementedError("fa_b200.sdpa: only self-attention and single-row decode are covered")
+
+
+__all__ = ["prefill", "decode", "sdpa", "FaError"]

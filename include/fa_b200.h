@@ -158,6 +158,53 @@ int    fa_decode(const fa_decode_args* args);
 #define FA_DECODE_STATIC_SCRATCH_BYTES (8u * 1024u * 1024u + 512u * 1024u)
 int fa_decode_static(const fa_decode_args* args);
 
+/* ---------------------------------------------------------------------------
+ * fa_decode_gqa: grouped-query / multi-query decode over a strided KV cache.
+ * No reference counterpart (the reference has one K/V head per query head and
+ * dense tensors, include/flash_attention.h:46-61); the result is defined as
+ * cpu_attention (src/demo.cu:28-70) applied per query head hq, one query row,
+ * with K and V of KV head hq / (num_q_heads / num_kv_heads).
+ *
+ *   q   [B, Hq, D] dense;  o [B, Hq, D];  lse [B, Hq] (optional, natural log)
+ *   k,v key r of KV head h of sequence b at element offset
+ *           b * kv_batch_stride + h * kv_head_stride + r * kv_row_stride
+ *       (rows of D contiguous elements; the three strides multiples of 8 elements;
+ *        all zero = dense [B, Hkv, Skv, D]).  A cache laid out [B, Skv, Hkv, D] is
+ *        kv_row_stride = Hkv*D, kv_head_stride = D, kv_batch_stride = Skv*Hkv*D.
+ *
+ * The group of num_q_heads / num_kv_heads (<= 128) query heads that share a KV
+ * head occupies the rows of one tensor-core query tile, so K and V stream from
+ * HBM once per KV head whatever the group size.  The KV length is split over
+ * CTAs; partial results go through `workspace`
+ * (>= fa_decode_workspace_bytes(B, Hq, D, splits) with
+ * splits = num_splits, or fa_decode_gqa_default_splits(...) when num_splits is 0)
+ * and are merged by the combine kernel.
+ * ------------------------------------------------------------------------- */
+typedef struct fa_decode_gqa_args {
+    const void* q;
+    const void* k;
+    const void* v;
+    void*       o;
+    float*      lse;              /* optional */
+    int         batch_size;
+    int         num_q_heads;
+    int         num_kv_heads;     /* divides num_q_heads */
+    int         seq_len_kv;
+    int         d_head;           /* 64 or 128 */
+    float       scale;
+    int         dtype;            /* FA_DTYPE_F16 or FA_DTYPE_BF16 */
+    int         num_splits;       /* 0 = library chooses; else 1..FA_MAX_SPLITS */
+    long long   kv_batch_stride;  /* elements; see above */
+    long long   kv_head_stride;
+    long long   kv_row_stride;
+    void*       workspace;
+    size_t      workspace_bytes;
+    void*       stream;
+} fa_decode_gqa_args;
+
+int fa_decode_gqa_default_splits(int batch_size, int num_kv_heads, int seq_len_kv);
+int fa_decode_gqa(const fa_decode_gqa_args* args);
+
 /*
  * LSE merge of n_parts partial results (the exchange step of KV-sequence
  * sharded decode: each rank's (o_f32, lse) gathered into one local buffer).

@@ -1,0 +1,51 @@
+"""torch.ops.fa_b200.* against torch's own scaled_dot_product_attention evaluated in fp32 on the CPU
+(fp32 reference of the same op; tolerance: the 16-bit rounding of P and O, 2e-3 abs for fp16)."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def op(fa):
+    import __graft_entry__ as ge
+    return ge.load_module("torch_op")
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float16, 2e-3), (torch.bfloat16, 1.6e-2)])
+@pytest.mark.parametrize("causal", [False, True])
+def test_prefill_matches_sdpa(op, dev, dtype, tol, causal):
+    g = torch.Generator().manual_seed(5)
+    q, k, v = (torch.randn((2, 3, 200, 64), generator=g).to(dtype) for _ in range(3))
+    ref = torch.nn.functional.scaled_dot_product_attention(q.float(), k.float(), v.float(), is_causal=causal)
+    out = op.sdpa(q.to(dev), k.to(dev), v.to(dev), is_causal=causal)
+    assert out.dtype == dtype and out.shape == q.shape
+    assert (out.float().cpu() - ref).abs().max().item() < tol
+    o2, lse = torch.ops.fa_b200.prefill(q.to(dev), k.to(dev), v.to(dev), 0.125, causal)
+    s = (q.float() @ k.float().transpose(-1, -2)) * 0.125
+    if causal:
+        s = s.masked_fill(torch.ones(200, 200, dtype=torch.bool).triu(1), float("-inf"))
+    assert (lse.cpu() - torch.logsumexp(s, -1)).abs().max().item() < 1e-3
+    assert torch.equal(o2, out)
+
+
+def test_decode_matches_sdpa(op, dev):
+    g = torch.Generator().manual_seed(6)
+    q = torch.randn((2, 4, 1, 128), generator=g).half()
+    k, v = (torch.randn((2, 4, 3000, 128), generator=g).half() for _ in range(2))
+    ref = torch.nn.functional.scaled_dot_product_attention(q.float(), k.float(), v.float())
+    out = op.sdpa(q.to(dev), k.to(dev), v.to(dev))
+    assert (out.float().cpu() - ref).abs().max().item() < 2e-3
+
+
+def test_non_contiguous_inputs_and_side_stream(op, dev):
+    g = torch.Generator().manual_seed(7)
+    base = torch.randn((2, 130, 3, 64), generator=g).half().to(dev)       # [B, S, H, D]
+    q = base.permute(0, 2, 1, 3)                                          # [B, H, S, D] view
+    ref = torch.nn.functional.scaled_dot_product_attention(q.float().cpu(), q.float().cpu(), q.float().cpu())
+    st = torch.cuda.Stream(device=dev)
+    st.wait_stream(torch.cuda.current_stream(dev))
+    with torch.cuda.stream(st):
+        out = op.sdpa(q, q, q)
+    st.synchronize()
+    assert (out.float().cpu() - ref).abs().max().item() < 2e-3
