@@ -457,6 +457,16 @@ FA_EXPORT int fa_decode_gqa(const fa_decode_gqa_args* a) {
         hs = (long long)a->seq_len_kv * a->d_head;
         bs = hs * a->num_kv_heads;
     }
+    const bool paged = a->block_table != nullptr;
+    if (paged) {
+        const int ps = a->page_size;
+        if (ps < 16 || (ps & (ps - 1)) != 0 || a->num_pages <= 0) return FA_ERR_INVALID_ARGUMENT;
+        if ((long long)a->block_table_stride * ps < a->seq_len_kv) return FA_ERR_INVALID_ARGUMENT;
+        if (a->kv_row_stride < a->d_head || a->kv_head_stride <= 0 || a->kv_page_stride <= 0)
+            return FA_ERR_INVALID_ARGUMENT;
+        if ((a->kv_row_stride % 8) || (a->kv_head_stride % 8) || (a->kv_page_stride % 8)) return FA_ERR_MISALIGNED;
+        rs = a->kv_row_stride; hs = a->kv_head_stride; bs = 8;
+    }
     if (rs < a->d_head || hs <= 0 || bs <= 0) return FA_ERR_INVALID_ARGUMENT;
     if ((rs % 8) || (hs % 8) || (bs % 8)) return FA_ERR_MISALIGNED;
     if (!aligned16(a->q) || !aligned16(a->k) || !aligned16(a->v) || !aligned16(a->o)) return FA_ERR_MISALIGNED;
@@ -483,6 +493,9 @@ FA_EXPORT int fa_decode_gqa(const fa_decode_gqa_args* a) {
     g.kv_len = a->seq_len_kv; g.d_head = a->d_head; g.dtype = a->dtype;
     g.n_splits = splits; g.tiles_per_split = tps;
     g.row_stride = rs; g.head_stride = hs; g.batch_stride = bs;
+    g.seq_lens = a->seq_lens;
+    g.block_table = a->block_table; g.table_stride = a->block_table_stride;
+    g.page_size = paged ? a->page_size : 0; g.n_pages = a->num_pages; g.page_stride = a->kv_page_stride;
     g.scale = a->scale; g.stream = stream;
     int rc = launch_decode_gqa(g, st);
     if (rc != FA_OK) return rc;

@@ -69,6 +69,10 @@ struct GqaLaunch {
     int batch, n_kv_heads, group, kv_len, d_head, dtype;
     int n_splits, tiles_per_split;
     long long row_stride, head_stride, batch_stride;   // of the KV cache, in elements
+    const int* seq_lens;                      // [batch] or null
+    const int* block_table;                   // paged cache: [batch][table_stride] page numbers, or null
+    int table_stride, page_size, n_pages;
+    long long page_stride;                    // elements between pages
     float scale;
     cudaStream_t stream;
 };

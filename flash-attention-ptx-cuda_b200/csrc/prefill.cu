@@ -141,29 +141,40 @@ struct PrefillSmem {
 struct GqaDev {
     float* o_part;          // [row][split][D] fp32, row = (batch x KV head) * group + query head in group
     float* lse_part;        // [row][split]
-    int n_splits, tiles_per_split, n_tiles, group, n_hkv;
+    int n_splits, tiles_per_split, group, n_hkv;
+    const int* seq_lens;    // per-sequence KV lengths, or null: every sequence has seq_len keys
+    const int* block_table; // paged cache: [batch][table_stride] page numbers, or null
+    int table_stride;
+    int page_shift;         // log2(page size)
 };
 
 // Work list: item index -> (query tile, head), heaviest first when causal.  In grouped-query
 // decode mode an item is (batch x KV head, KV split): key tiles [t0, t0 + n_kv) of that head.
-struct Item { int q_start, bh, n_kv, t0, split; };
+struct Item { int q_start, bh, n_kv, t0, split, kv_len; bool empty; };
 
 template <bool CAUSAL, bool GQA>
 __device__ __forceinline__ bool get_item(int k, int n_items, int n_bh, int n_qtiles, int seq_len,
                                          const GqaDev& gq, Item& it) {
     const int G = gridDim.x, c = blockIdx.x;
     if constexpr (GQA) {
-        const int idx = k * G + c;                    // items are equal: plain round-robin
+        const int idx = k * G + c;                    // items are (nearly) equal: plain round-robin
+        it.empty = false;
         if (idx >= n_items) return false;
         it.bh = idx / gq.n_splits;
         it.split = idx - it.bh * gq.n_splits;
         it.t0 = it.split * gq.tiles_per_split;
-        it.n_kv = min(gq.tiles_per_split, gq.n_tiles - it.t0);
+        it.kv_len = gq.seq_lens ? min(seq_len, max(0, __ldg(gq.seq_lens + it.bh / gq.n_hkv))) : seq_len;
+        it.n_kv = min(gq.tiles_per_split, (it.kv_len + kBN - 1) / kBN - it.t0);
         it.q_start = 0;
-        return true;
+        // a split that lies wholly past the end of a short sequence: no role touches it, the
+        // epilogue warps only record an empty partial
+        it.empty = it.n_kv <= 0;
+        return !it.empty;
     }
     it.t0 = 0;
     it.split = 0;
+    it.kv_len = seq_len;
+    it.empty = false;
     const int idx = (k & 1) ? k * G + (G - 1 - c) : k * G + c;     // boustrophedon deal
     if (idx >= n_items) return false;
     const int qt = CAUSAL ? (n_qtiles - 1 - idx / n_bh) : (idx / n_bh);
@@ -206,6 +217,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     __shared__ __align__(8) uint64_t bar_pf[kNU];            // P of the tile in score buffer u is in TMEM
     __shared__ __align__(8) uint64_t bar_v8f[2], bar_v8e[2];
     __shared__ __align__(8) uint64_t bar_epi;                // rendezvous of the warps that run the epilogue
+    __shared__ __align__(8) uint64_t bar_vraw;               // grouped-query decode: a V tile that still needs its tail rows cleared
     // per item parity and row: {max in use (float bits), index of the tile it was decided for};
     // written with one 8-byte store by the tile's owner, polled by the owner of the next tile
     __shared__ __align__(8) uint2 m_slot[2][128];
@@ -238,6 +250,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             mbar_init(smem_u32(&bar_v8e[i]), 128);
         }
         mbar_init(smem_u32(&bar_epi), 4);
+        mbar_init(smem_u32(&bar_vraw), 1);
         for (int i = 0; i < 2; i++) { mbar_init(smem_u32(&bar_stats[i]), 8); mbar_init(smem_u32(&bar_stats_free[i]), 4); }
         abort_flag = 0;
         fence_mbar_init();
@@ -255,6 +268,27 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     const uint32_t tmem = tmem_slot;
     const int n_rounds = (n_items + gridDim.x - 1) / gridDim.x;
 
+    // Grouped-query decode: one 128-key tile of K or V of (batch, KV head) from the cache.  Dense or
+    // strided cache: tensor map (d, key, KV head, batch).  Paged cache: tensor map (d, key in page,
+    // KV head, page); a tile is one box inside a page, or 128 / page_size boxes of one page each;
+    // pages past the end of the sequence are fetched at coordinate -1, which reads as zero.
+    auto load_cache_tile = [&](uint32_t dst, const CUtensorMap* tm, uint32_t bar, const Item& it, int j) {
+        const int hkv = it.bh % gq.n_hkv, b = it.bh / gq.n_hkv;
+        const int r0 = (it.t0 + j) * kBN;
+        if (gq.block_table == nullptr) {
+            for (int bx = 0; bx < NBOX; bx++) tma_load_4d(dst + bx * L::kBox, tm, bar, bx * 64, r0, hkv, b);
+        } else {
+            const int ps = 1 << gq.page_shift;
+            const int rows = min(ps, kBN);            // rows per box
+            const int* tbl = gq.block_table + static_cast<size_t>(b) * gq.table_stride;
+            for (int i = 0; i < kBN / rows; i++) {
+                const int rr = r0 + i * rows;
+                const int page = rr < it.kv_len ? __ldg(tbl + (rr >> gq.page_shift)) : -1;
+                for (int bx = 0; bx < NBOX; bx++)
+                    tma_load_4d(dst + bx * L::kBox + i * rows * 128, tm, bar, bx * 64, rr & (ps - 1), hkv, page);
+            }
+        }
+    };
     if (warp >= 12) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsHelper));
     else if (warp >= 8) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsOther));
     if (warp == 8) {
@@ -278,11 +312,10 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                     // the slot was last read by Q K^T of tile g - NK
                     if (g >= NK && !mbar_wait(smem_u32(&bar_qk[(g - NK) % kRing]), ((g - NK) / kRing) & 1, ctl, kBarKEmpty)) { ok = false; break; }
                     mbar_arrive_expect_tx(smem_u32(&bar_kf[sk]), L::kKBytes);
-                    for (int b = 0; b < NLOAD; b++) {
-                        if constexpr (GQA)          // KV cache map: (d, key, KV head, batch)
-                            tma_load_4d(k_s + sk * L::kKBytes + b * L::kBox, &tm_k, smem_u32(&bar_kf[sk]),
-                                        b * XSTEP, (it.t0 + j) * kBN, it.bh % gq.n_hkv, it.bh / gq.n_hkv);
-                        else
+                    if constexpr (GQA) {
+                        load_cache_tile(k_s + sk * L::kKBytes, &tm_k, smem_u32(&bar_kf[sk]), it, j);
+                    } else {
+                        for (int b = 0; b < NLOAD; b++)
                             tma_load_3d(k_s + sk * L::kKBytes + b * L::kBox, &tm_k, smem_u32(&bar_kf[sk]),
                                         b * XSTEP, j * kBN, it.bh);
                     }
@@ -294,7 +327,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     } else if (warp == 11) {
         // ------------------------------------------------------------ TMA producer: V
         if (lane == 0) {
-            int g = 0;
+            int g = 0, n_scrub = 0;
             bool ok = true;
             for (int r = 0; ok && r < n_rounds; r++) {
                 Item it;
@@ -310,12 +343,34 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                         const int sv = g % NV;
                         // the slot was last read by P V of tile g - NV
                         if (g >= NV && !mbar_wait(smem_u32(&bar_pvd[(g - NV) % kRing]), ((g - NV) / kRing) & 1, ctl, kBarVEmpty)) { ok = false; break; }
-                        mbar_arrive_expect_tx(smem_u32(&bar_vf[sv]), L::kVBytes);
-                        for (int b = 0; b < NBOX; b++) {
-                            if constexpr (GQA)
-                                tma_load_4d(v_s + sv * L::kVBytes + b * L::kBox, &tm_v, smem_u32(&bar_vf[sv]),
-                                            b * 64, (it.t0 + j) * kBN, it.bh % gq.n_hkv, it.bh / gq.n_hkv);
-                            else
+                        if constexpr (GQA) {
+                            // Rows of the sequence's last tile past its end are stale cache contents when the
+                            // cache is paged or longer than the sequence (a dense cache reads them as zero).
+                            // P is exactly 0 there, but 0 x NaN would still poison O, so those rows of V are
+                            // cleared before the P V issuer may see the tile: the load completes on a private
+                            // barrier, this thread clears the rows and then releases the tile itself.
+                            const int valid = it.kv_len - (it.t0 + j) * kBN;      // rows of this tile inside the sequence
+                            const bool scrub = valid < kBN && (gq.seq_lens != nullptr || gq.block_table != nullptr);
+                            const uint32_t vdst = v_s + sv * L::kVBytes;
+                            if (!scrub) {
+                                mbar_arrive_expect_tx(smem_u32(&bar_vf[sv]), L::kVBytes);
+                                load_cache_tile(vdst, &tm_v, smem_u32(&bar_vf[sv]), it, j);
+                            } else {
+                                mbar_arrive_expect_tx(smem_u32(&bar_vraw), L::kVBytes);
+                                load_cache_tile(vdst, &tm_v, smem_u32(&bar_vraw), it, j);
+                                if (!mbar_wait(smem_u32(&bar_vraw), n_scrub & 1, ctl, kBarVFull)) { ok = false; break; }
+                                n_scrub++;
+                                for (int row = valid; row < kBN; row++)
+                                    for (int b = 0; b < NBOX; b++)
+                                        for (int q16 = 0; q16 < 8; q16++)
+                                            asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(
+                                                vdst + b * L::kBox + row * 128 + q16 * 16), "r"(0u) : "memory");
+                                fence_proxy_async_smem();
+                                mbar_arrive(smem_u32(&bar_vf[sv]));
+                            }
+                        } else {
+                            mbar_arrive_expect_tx(smem_u32(&bar_vf[sv]), L::kVBytes);
+                            for (int b = 0; b < NBOX; b++)
                                 tma_load_3d(v_s + sv * L::kVBytes + b * L::kBox, &tm_v, smem_u32(&bar_vf[sv]),
                                             b * 64, j * kBN, it.bh);
                         }
@@ -424,7 +479,18 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         bool ok = true;
         for (int r = 0; ok && r < n_rounds; r++) {
             Item it;
-            if (!get_item<CAUSAL, GQA>(r, n_items, n_bh, n_qtiles, seq_len, gq, it)) continue;
+            if (!get_item<CAUSAL, GQA>(r, n_items, n_bh, n_qtiles, seq_len, gq, it)) {
+                if constexpr (GQA) {
+                    // a KV split past the end of a short sequence: weight zero in the merge
+                    if (it.empty && r_in_tile < gq.group) {
+                        const size_t pidx = (static_cast<size_t>(it.bh) * gq.group + r_in_tile) * gq.n_splits + it.split;
+                        gq.lse_part[pidx] = -INFINITY;
+                        float4* dst = reinterpret_cast<float4*>(gq.o_part + pidx * D);
+                        for (int e = 0; e < D / 4; e++) dst[e] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                    }
+                }
+                continue;
+            }
             if constexpr (FP8) {
                 // ---- e4m3 -> fp16 conversion of the item's V tiles (exact)
                 for (int j = 0; j < it.n_kv; j++, g++) {
@@ -550,8 +616,8 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             Item it;
             if (!get_item<CAUSAL, GQA>(r, n_items, n_bh, n_qtiles, seq_len, gq, it)) continue;
             const int row = it.q_start + r_in_tile;
-            const int row_limit = CAUSAL ? min(seq_len, row + 1) : seq_len;   // keys [0,row_limit) visible
-            const int tile_min_limit = CAUSAL ? min(seq_len, it.q_start + 1) : seq_len;
+            const int row_limit = CAUSAL ? min(seq_len, row + 1) : it.kv_len;   // keys [0,row_limit) visible
+            const int tile_min_limit = CAUSAL ? min(seq_len, it.q_start + 1) : it.kv_len;
             float scale_log2 = scale_log2_in;
             if constexpr (FP8) scale_log2 *= q_scale[it.bh] * k_scale[it.bh];
             const uint64_t scale2 = pack2(scale_log2, scale_log2);
@@ -739,11 +805,13 @@ int launch_gqa_instance(const GqaLaunch& g, DeviceState* st, const CUtensorMap& 
         configured[st->device] = true;
     }
     const int n_bh = g.batch * g.n_kv_heads;
-    const int n_tiles = (g.kv_len + kBN - 1) / kBN;
     const long long n_items = (long long)n_bh * g.n_splits;
     if (n_items > 0x7FFFFFFFll) return FA_ERR_INVALID_ARGUMENT;
     const unsigned grid = (unsigned)(n_items < st->sm_count ? n_items : st->sm_count);
-    const GqaDev gq{g.o_part, g.lse_part, g.n_splits, g.tiles_per_split, n_tiles, g.group, g.n_kv_heads};
+    int page_shift = 0;
+    while ((1 << page_shift) < g.page_size) page_shift++;
+    const GqaDev gq{g.o_part, g.lse_part, g.n_splits, g.tiles_per_split, g.group, g.n_kv_heads,
+                    g.seq_lens, g.block_table, g.table_stride, page_shift};
     kernel<<<grid, kThreads, L::kTotal, g.stream>>>(tq, tk, tv, tq, nullptr, g.kv_len, n_bh, 1, (int)n_items,
                                                     g.scale * kLog2e, nullptr, nullptr, nullptr, st->status, gq);
     FA_CUDA_TRY(cudaGetLastError());
@@ -778,10 +846,16 @@ int launch_decode_gqa(const GqaLaunch& g, DeviceState* st) {
     int rc;
     // Q [B, Hq, D] seen as (batch x KV head) tiles of `group` rows; rows past the group read as zero
     if ((rc = make_tensor_map_3d(&tq, g.q, g.dtype, g.d_head, g.group, n_bh, 64, kBM)) != FA_OK) return rc;
-    if ((rc = make_tensor_map_4d(&tk, g.k, g.dtype, g.d_head, g.kv_len, g.n_kv_heads, g.batch, g.row_stride,
-                                 g.head_stride, g.batch_stride, 64, kBN)) != FA_OK) return rc;
-    if ((rc = make_tensor_map_4d(&tv, g.v, g.dtype, g.d_head, g.kv_len, g.n_kv_heads, g.batch, g.row_stride,
-                                 g.head_stride, g.batch_stride, 64, kBN)) != FA_OK) return rc;
+    // dense / strided cache: (d, key, KV head, batch); paged: (d, key in page, KV head, page)
+    const bool paged = g.block_table != nullptr;
+    const uint64_t rows = paged ? (uint64_t)g.page_size : (uint64_t)g.kv_len;
+    const uint64_t blocks = paged ? (uint64_t)g.n_pages : (uint64_t)g.batch;
+    const uint64_t bstride = paged ? (uint64_t)g.page_stride : (uint64_t)g.batch_stride;
+    const uint32_t box_rows = paged && g.page_size < kBN ? (uint32_t)g.page_size : (uint32_t)kBN;
+    if ((rc = make_tensor_map_4d(&tk, g.k, g.dtype, g.d_head, rows, g.n_kv_heads, blocks, g.row_stride,
+                                 g.head_stride, bstride, 64, box_rows)) != FA_OK) return rc;
+    if ((rc = make_tensor_map_4d(&tv, g.v, g.dtype, g.d_head, rows, g.n_kv_heads, blocks, g.row_stride,
+                                 g.head_stride, bstride, 64, box_rows)) != FA_OK) return rc;
     const bool bf = g.dtype == FA_DTYPE_BF16;
     if (g.d_head == 64) return bf ? launch_gqa_instance<64, true>(g, st, tq, tk, tv) : launch_gqa_instance<64, false>(g, st, tq, tk, tv);
     return bf ? launch_gqa_instance<128, true>(g, st, tq, tk, tv) : launch_gqa_instance<128, false>(g, st, tq, tk, tv);

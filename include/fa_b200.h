@@ -172,6 +172,16 @@ int fa_decode_static(const fa_decode_args* args);
  *        all zero = dense [B, Hkv, Skv, D]).  A cache laid out [B, Skv, Hkv, D] is
  *        kv_row_stride = Hkv*D, kv_head_stride = D, kv_batch_stride = Skv*Hkv*D.
  *
+ *   Paged cache (block_table != NULL): k and v point at pools of pages of
+ *       page_size keys (a power of two >= 16); key r of KV head h of sequence b
+ *       lives in page p = block_table[b * block_table_stride + r / page_size] at
+ *           p * kv_page_stride + (r % page_size) * kv_row_stride + h * kv_head_stride
+ *       (kv_batch_stride is ignored; num_pages is the size of the pool).
+ *   seq_lens (optional, device, [B]): KV length of each sequence, clamped to
+ *       [0, seq_len_kv]; seq_len_kv then is the maximum and sizes the splits.  A
+ *       sequence of length 0 yields O = 0 and LSE = -inf.  Cache contents past a
+ *       sequence's end are never used (they may be uninitialised).
+ *
  * The group of num_q_heads / num_kv_heads (<= 128) query heads that share a KV
  * head occupies the rows of one tensor-core query tile, so K and V stream from
  * HBM once per KV head whatever the group size.  The KV length is split over
@@ -197,6 +207,12 @@ typedef struct fa_decode_gqa_args {
     long long   kv_batch_stride;  /* elements; see above */
     long long   kv_head_stride;
     long long   kv_row_stride;
+    const int*  block_table;      /* device; NULL = not paged */
+    int         block_table_stride;
+    int         page_size;
+    int         num_pages;
+    long long   kv_page_stride;
+    const int*  seq_lens;         /* device; NULL = every sequence has seq_len_kv keys */
     void*       workspace;
     size_t      workspace_bytes;
     void*       stream;

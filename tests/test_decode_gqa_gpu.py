@@ -123,3 +123,88 @@ def test_gqa_argument_errors(fa, dev):
     assert fa.decode_gqa_raw(t, t, t, t, None, 1, 4, 2, 128, 64, 0.1, dtype="f16", workspace=ws,
                              workspace_bytes=16) == fa.FA_ERR_WORKSPACE
     assert fa.decode_gqa_raw(t, t, t, t, None, 1, 256, 1, 128, 64, 0.1, **ok) == fa.FA_ERR_UNSUPPORTED      # group > 128
+
+
+def oracle_ragged(oracle, q, k, v, lens, scale):
+    """Per sequence its own KV length (0 allowed: O = 0, LSE = -inf)."""
+    b, hq, d = q.shape
+    o = np.zeros((b, hq, d), np.float32)
+    l = np.full((b, hq), -np.inf, np.float32)
+    for i in range(b):
+        if lens[i] > 0:
+            oi, li = oracle_gqa(oracle, q[i:i + 1], k[i:i + 1, :, :lens[i]], v[i:i + 1, :, :lens[i]], scale)
+            o[i], l[i] = oi[0], li[0]
+    return o, l
+
+
+@pytest.mark.parametrize("page_size", [16, 64, 128, 256])
+def test_gqa_paged_cache_with_sequence_lengths(fa, oracle, dev, page_size):
+    """Pages scattered through a pool whose unused parts hold NaN; ragged sequence lengths,
+    one of them zero, one ending exactly on a page boundary."""
+    b, hq, hkv, d = 4, 8, 2, 128
+    lens = [1000, 0, 512, 77]
+    smax = 1024
+    scale = 1.0 / np.sqrt(d)
+    q, k, v = make(oracle, 300 + page_size, b, hq, hkv, smax, d, "f16")
+    o_ref, l_ref = oracle_ragged(oracle, q, k, v, lens, scale)
+
+    pages_per_seq = smax // page_size
+    n_pages = b * pages_per_seq + 5
+    rng = np.random.default_rng(page_size)
+    perm = rng.permutation(n_pages)[: b * pages_per_seq].reshape(b, pages_per_seq)
+    # pool layout [page][key in page][KV head][D]
+    kp = torch.full((n_pages, page_size, hkv, d), float("nan"), device=dev, dtype=torch.float16)
+    vp = torch.full((n_pages, page_size, hkv, d), float("nan"), device=dev, dtype=torch.float16)
+    table = np.full((b, pages_per_seq), -1, np.int32)
+    dk, dv = to_dev(k, "f16", dev), to_dev(v, "f16", dev)
+    for i in range(b):
+        for pg in range((lens[i] + page_size - 1) // page_size):
+            r0, r1 = pg * page_size, min((pg + 1) * page_size, lens[i])
+            table[i, pg] = perm[i, pg]
+            kp[perm[i, pg], : r1 - r0] = dk[i, :, r0:r1].permute(1, 0, 2)
+            vp[perm[i, pg], : r1 - r0] = dv[i, :, r0:r1].permute(1, 0, 2)
+    dtab = torch.from_numpy(table).to(dev)
+    dlens = torch.tensor(lens, device=dev, dtype=torch.int32)
+    dq = to_dev(q, "f16", dev)
+    do = torch.full((b, hq, d), float("nan"), device=dev, dtype=torch.float16)
+    dl = torch.full((b, hq), float("nan"), device=dev, dtype=torch.float32)
+    splits = fa.decode_gqa_default_splits(b, hkv, smax)
+    wsb = fa.decode_workspace_bytes(b, hq, d, splits)
+    ws = torch.full((wsb // 4,), float("nan"), device=dev, dtype=torch.float32)
+    fa.decode_gqa(dq, kp, vp, do, dl, b, hq, hkv, smax, d, float(scale), dtype="f16",
+                  kv_strides=(0, d, hkv * d), block_table=dtab, block_table_stride=pages_per_seq,
+                  page_size=page_size, num_pages=n_pages, kv_page_stride=page_size * hkv * d, seq_lens=dlens,
+                  workspace=ws, workspace_bytes=wsb)
+    torch.cuda.synchronize()
+    assert fa.device_status() == 0
+    o, l = do.float().cpu().numpy(), dl.cpu().numpy()
+    assert np.isfinite(o).all()
+    assert np.abs(o - o_ref).max() < 2e-3
+    assert l[1].tolist() == [-np.inf] * hq
+    live = np.isfinite(l_ref)
+    assert np.abs(l[live] - l_ref[live]).max() < 1e-3
+
+
+def test_gqa_sequence_lengths_on_a_dense_cache(fa, oracle, dev):
+    """seq_lens with a plain [B, Hkv, Smax, D] cache whose tail rows hold NaN; several splits, so
+    some (sequence, split) pairs are empty."""
+    b, hq, hkv, d, smax = 3, 4, 1, 64, 4096
+    lens = [4096, 130, 2049]
+    scale = 1.0 / np.sqrt(d)
+    q, k, v = make(oracle, 501, b, hq, hkv, smax, d, "f16")
+    o_ref, l_ref = oracle_ragged(oracle, q, k, v, lens, scale)
+    dq, dk, dv = (to_dev(x, "f16", dev) for x in (q, k, v))
+    for i in range(b):
+        dk[i, :, lens[i]:] = float("nan")
+        dv[i, :, lens[i]:] = float("nan")
+    dlens = torch.tensor(lens, device=dev, dtype=torch.int32)
+    do = torch.full((b, hq, d), float("nan"), device=dev, dtype=torch.float16)
+    dl = torch.full((b, hq), float("nan"), device=dev, dtype=torch.float32)
+    wsb = fa.decode_workspace_bytes(b, hq, d, 8)
+    ws = torch.full((wsb // 4,), float("nan"), device=dev, dtype=torch.float32)
+    fa.decode_gqa(dq, dk, dv, do, dl, b, hq, hkv, smax, d, float(scale), dtype="f16", num_splits=8,
+                  seq_lens=dlens, workspace=ws, workspace_bytes=wsb)
+    torch.cuda.synchronize()
+    assert fa.device_status() == 0
+    assert np.abs(do.float().cpu().numpy() - o_ref).max() < 2e-3
+    assert np.abs(dl.cpu().numpy() - l_ref).max() < 1e-3
