@@ -356,7 +356,7 @@ def run_b200_arm(args, rank, local_rank, world):
     # ---- the other BASELINE configurations (short runs, reported beside the headline)
     other = None
     if not args.no_extra:
-        other = run_other_configs(fa, torch, dev, stream, peaks)
+        other = run_other_configs(fa, torch, dev, stream, peaks, args.gqa_batch)
 
     clocks = sampler.summary()
     cpu_baseline = None
@@ -444,7 +444,7 @@ def run_kv_sharded_decode(fa, ge, torch, dist, dev, stream, rank, world, peaks, 
                     "launches and the all-gather round trip", "scaling": "strong"}
 
 
-def run_other_configs(fa, torch, dev, stream, peaks):
+def run_other_configs(fa, torch, dev, stream, peaks, gqa_batch=0):
     """Config 3 (bf16 B1 H32 S8192 D128, causal and not) and config 5 (e4m3 B8 H16 S4096 D128
     causal): device-resident, 3 warm-up + 10 timed launches each, inputs 0.2-0.3 GB (> L2)."""
     out = {}
@@ -490,7 +490,8 @@ def run_other_configs(fa, torch, dev, stream, peaks):
 
     # grouped-query decode over a [B, Skv, Hkv, D] cache: the group's query heads ride in the rows of
     # the tensor-core query tile, K and V stream once per KV head (HBM-bound: report GB/s)
-    for (b, hq, hkv, skv, d) in ((32, 32, 8, 16384, 128), (32, 32, 1, 32768, 128)):
+    gb = gqa_batch or 32
+    for (b, hq, hkv, skv, d) in ((gb, 32, 8, 16384, 128), (gb, 32, 1, 32768, 128)):
         kc = torch.randn((b, skv, hkv, d), device=dev, dtype=torch.float32).to(torch.float16)
         vc = torch.randn((b, skv, hkv, d), device=dev, dtype=torch.float32).to(torch.float16)
         qg = torch.randn((b, hq, d), device=dev, dtype=torch.float32).to(torch.float16)
@@ -570,6 +571,8 @@ def main():
                     help="profiling only: override the prefill batch (the line is then not the headline)")
     ap.add_argument("--decode-batch", type=int, default=0,
                     help="profiling only: override the decode batch")
+    ap.add_argument("--gqa-batch", type=int, default=0,
+                    help="profiling only: override the batch of the grouped-query decode cases")
     ap.add_argument("--no-cpu", action="store_true")
     args = ap.parse_args()
     if args.batch:
