@@ -36,7 +36,8 @@ DTYPES = {"f16": FA_DTYPE_F16, "bf16": FA_DTYPE_BF16, "e4m3": FA_DTYPE_E4M3}
 # Every symbol include/fa_b200.h declares; the CPU-only tests check they all resolve.
 EXPORTED_SYMBOLS = (
     "fa_prefill", "fa_prefill_host", "fa_decode", "fa_decode_static", "fa_decode_workspace_bytes",
-    "fa_decode_default_splits", "fa_decode_gqa", "fa_decode_gqa_default_splits", "fa_combine", "fa_kat",
+    "fa_decode_default_splits", "fa_decode_gqa", "fa_decode_gqa_default_splits", "fa_backward",
+    "fa_backward_workspace_bytes", "fa_combine", "fa_kat",
     "fa_device_status",
     "fa_clear_device_status", "fa_error_string", "fa_last_cuda_error", "fa_version",
 )
@@ -85,6 +86,18 @@ class DecodeGqaArgs(ctypes.Structure):
     ]
 
 
+class BackwardArgs(ctypes.Structure):
+    """Mirror of ``fa_backward_args`` (include/fa_b200.h)."""
+    _fields_ = [
+        ("q", ctypes.c_void_p), ("k", ctypes.c_void_p), ("v", ctypes.c_void_p), ("o", ctypes.c_void_p),
+        ("d_o", ctypes.c_void_p), ("lse", ctypes.c_void_p),
+        ("dq", ctypes.c_void_p), ("dk", ctypes.c_void_p), ("dv", ctypes.c_void_p),
+        ("batch_size", ctypes.c_int), ("num_heads", ctypes.c_int), ("seq_len", ctypes.c_int),
+        ("d_head", ctypes.c_int), ("scale", ctypes.c_float), ("causal", ctypes.c_int), ("dtype", ctypes.c_int),
+        ("workspace", ctypes.c_void_p), ("workspace_bytes", ctypes.c_size_t), ("stream", ctypes.c_void_p),
+    ]
+
+
 class FaError(RuntimeError):
     def __init__(self, code: int, what: str):
         super().__init__(f"{what}: {error_string(code)} ({code})"
@@ -119,6 +132,10 @@ def lib() -> ctypes.CDLL:
         l.fa_decode_gqa.argtypes = [ctypes.POINTER(DecodeGqaArgs)]
         l.fa_decode_gqa_default_splits.restype = ctypes.c_int
         l.fa_decode_gqa_default_splits.argtypes = [ctypes.c_int] * 3
+        l.fa_backward.restype = ctypes.c_int
+        l.fa_backward.argtypes = [ctypes.POINTER(BackwardArgs)]
+        l.fa_backward_workspace_bytes.restype = ctypes.c_size_t
+        l.fa_backward_workspace_bytes.argtypes = [ctypes.c_int] * 3
         l.fa_combine.restype = ctypes.c_int
         l.fa_combine.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_int,
                                  ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int,
@@ -237,6 +254,26 @@ def decode_gqa(*args, **kw) -> None:
     rc = decode_gqa_raw(*args, **kw)
     if rc != FA_OK:
         raise FaError(rc, "fa_decode_gqa")
+
+
+def backward_workspace_bytes(batch_size, num_heads, seq_len) -> int:
+    return lib().fa_backward_workspace_bytes(batch_size, num_heads, seq_len)
+
+
+def backward_raw(q, k, v, o, d_o, lse, dq, dk, dv, batch_size, num_heads, seq_len, d_head, scale, causal,
+                 dtype="f16", workspace=None, workspace_bytes=0, stream=None) -> int:
+    """fa_backward on device buffers; returns the status code."""
+    a = BackwardArgs(_ptr(q), _ptr(k), _ptr(v), _ptr(o), _ptr(d_o), _ptr(lse), _ptr(dq), _ptr(dk), _ptr(dv),
+                     batch_size, num_heads, seq_len, d_head, scale, int(bool(causal)),
+                     DTYPES[dtype] if isinstance(dtype, str) else dtype, _ptr(workspace), workspace_bytes,
+                     _stream_handle(stream))
+    return lib().fa_backward(ctypes.byref(a))
+
+
+def backward(*args, **kw) -> None:
+    rc = backward_raw(*args, **kw)
+    if rc != FA_OK:
+        raise FaError(rc, "fa_backward")
 
 
 def combine(o_parts, lse_parts, n_parts, rows, d_head, o, lse, dtype="f16", stream=None) -> None:

@@ -1,0 +1,387 @@
+// Backward pass of the attention forward in prefill.cu: dQ, dK, dV from dO and
+// the log-sum-exp the forward saved.
+//
+// The reference has no backward; its forward kernel stores L "for the backward
+// pass" (kernels/flash_attention.cu:497).  The mathematics is that of its
+// forward (src/demo.cu:28-70) differentiated:
+//     P  = exp(S * scale - LSE),  S = Q K^T          (masked entries: P = 0)
+//     dV = P^T dO
+//     dP = dO V^T
+//     dS = P o (dP - delta) * scale,  delta_i = sum_d dO_id O_id
+//     dQ = dS K,   dK = dS^T Q
+//
+// Three kernels, no atomics:
+//   delta_kernel          delta = rowsum(dO o O), fp32.
+//   bwd_kernel<MODE 0>    one CTA per (key tile, head): K and V tiles stay in shared
+//                         memory, the query tiles stream past; per step
+//                         S^T = K Q^T and dP^T = V dO^T on the tensor core (so a
+//                         thread owns a KEY row in TMEM), P^T and dS^T are written back
+//                         to TMEM as 16-bit in place, then dV += P^T dO and dK += dS^T Q
+//                         with those as the TMEM operand.
+//   bwd_kernel<MODE 1>    one CTA per (query tile, head): Q and dO stay, the key tiles
+//                         stream; S = Q K^T, dP = dO V^T, dS in place, dQ += dS K.
+//                         (S and dP are computed twice overall; nothing is accumulated
+//                         across CTAs.)
+// Both modes are the same code: two stationary tiles A0, A1, two streamed tiles B0,
+// B1 per step, products T0 = A0 B0^T and T1 = A1 B1^T, accumulators fed from TMEM.
+//   warps 0-3  one thread per stationary row (TMEM lane): exponentials, dS, 16-bit
+//              write-back, final conversion and store of the accumulators.
+//   warp 4     lane 0 issues every TMA load and every tcgen05.mma; the products of
+//              step t+1 are issued once the accumulations of step t, which read the
+//              same TMEM columns, have completed.
+#include <cmath>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "host_common.h"
+#include "ptx.cuh"
+#include "tmem_ld.cuh"
+
+namespace fa {
+namespace {
+
+constexpr int kT = 128;                  // tile edge: stationary rows per CTA, streamed rows per step
+constexpr int kBwdThreads = 160;
+constexpr int kStages = 2;               // streamed (B0, B1) tile pairs in flight
+constexpr float kLog2e = 1.4426950408889634f;
+
+enum : int { kBwdBarA = 21, kBwdBarFull = 22, kBwdBarT = 23, kBwdBarP = 24, kBwdBarFree = 25, kBwdBarDone = 26 };
+
+template <int D>
+struct BwdSmem {
+    static constexpr int kNBox = D / 64;              // 64-column (128-byte) boxes per row
+    static constexpr int kBox = 128 * 128;            // one box: 128 rows x 128 bytes
+    static constexpr int kTile = kNBox * kBox;        // one 128 x D 16-bit tile
+    static constexpr int kTotal = 2 * kTile + kStages * 2 * kTile + 1024;
+};
+
+template <bool BF16>
+__global__ void delta_kernel(const uint16_t* __restrict__ o, const uint16_t* __restrict__ d_o,
+                             float* __restrict__ delta, long long n_rows, int d_head) {
+    const long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (row >= n_rows) return;
+    const int lane = threadIdx.x & 31;
+    float acc = 0.0f;
+    for (int c = lane * 2; c < d_head; c += 64) {
+        const uint32_t a = *reinterpret_cast<const uint32_t*>(o + row * d_head + c);
+        const uint32_t b = *reinterpret_cast<const uint32_t*>(d_o + row * d_head + c);
+        float a0, a1, b0, b1;
+        if constexpr (BF16) {
+            a0 = __uint_as_float(a << 16); a1 = __uint_as_float(a & 0xFFFF0000u);
+            b0 = __uint_as_float(b << 16); b1 = __uint_as_float(b & 0xFFFF0000u);
+        } else {
+            const float2 fa2 = __half22float2(*reinterpret_cast<const __half2*>(&a));
+            const float2 fb2 = __half22float2(*reinterpret_cast<const __half2*>(&b));
+            a0 = fa2.x; a1 = fa2.y; b0 = fb2.x; b1 = fb2.y;
+        }
+        acc = fmaf(a0, b0, fmaf(a1, b1, acc));
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+    if (lane == 0) delta[row] = acc;
+}
+
+// MODE 0: dK and dV of one key tile.  MODE 1: dQ of one query tile.
+template <int D, bool CAUSAL, bool BF16, int MODE>
+__global__ void __launch_bounds__(kBwdThreads, 1)
+bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+           const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
+           const float* __restrict__ lse, const float* __restrict__ delta, uint16_t* __restrict__ out0,
+           uint16_t* __restrict__ out1, int seq_len, int n_tiles, float scale, int* status) {
+    using L = BwdSmem<D>;
+    constexpr int NBOX = L::kNBox;
+    constexpr uint32_t FMT = BF16 ? kFmtBF16 : kFmtF16;
+    constexpr uint32_t T0_COL = 0, T1_COL = 128, ACC0_COL = 256, ACC1_COL = 256 + D;
+    static_assert(ACC1_COL + D <= 512, "TMEM columns");
+
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ __align__(8) uint64_t bar_a, bar_full[kStages], bar_free[kStages], bar_t, bar_p, bar_done;
+    __shared__ float st_lse[kT], st_delta[kT];          // MODE 0: statistics of the streamed query tile
+    __shared__ uint32_t tmem_slot;
+    __shared__ int abort_flag;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t a0_s = base, a1_s = base + L::kTile, b_s = base + 2 * L::kTile;
+    WaitCtl ctl{&abort_flag, status};
+
+    const int bh = blockIdx.x / n_tiles;
+    const int slot_x = blockIdx.x - bh * n_tiles;
+    // heavy tiles first under the causal mask: key tile 0 / the last query tile have the most steps
+    const int tile = (MODE == 0) ? slot_x : (n_tiles - 1 - slot_x);
+    const int first = (MODE == 0 && CAUSAL) ? tile : 0;                  // first streamed tile
+    const int n_steps = (MODE == 0) ? (n_tiles - first) : (CAUSAL ? tile + 1 : n_tiles);
+
+    if (tid == 0) {
+        mbar_init(smem_u32(&bar_a), 1);
+        for (int i = 0; i < kStages; i++) { mbar_init(smem_u32(&bar_full[i]), 1); mbar_init(smem_u32(&bar_free[i]), 1); }
+        mbar_init(smem_u32(&bar_t), 1);
+        mbar_init(smem_u32(&bar_p), 4);                  // one arrival per compute warp
+        mbar_init(smem_u32(&bar_done), 1);
+        abort_flag = 0;
+        fence_mbar_init();
+    }
+    __syncthreads();
+    if (warp == 4) tmem_alloc(smem_u32(&tmem_slot), 512);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = tmem_slot;
+
+    if (warp == 4) {
+        // ------------------------------------------------------------ TMA + MMA issue (one thread)
+        if (lane == 0) {
+            const CUtensorMap* ta0 = (MODE == 0) ? &tm_k : &tm_q;
+            const CUtensorMap* ta1 = (MODE == 0) ? &tm_v : &tm_do;
+            const CUtensorMap* tb0 = (MODE == 0) ? &tm_q : &tm_k;
+            const CUtensorMap* tb1 = (MODE == 0) ? &tm_do : &tm_v;
+            constexpr uint32_t idesc_t = make_idesc(kT, kT, FMT, FMT, kMajorK, kMajorK);
+            constexpr uint32_t idesc_acc = make_idesc(kT, D, FMT, FMT, kMajorK, kMajorMN);
+            constexpr uint64_t hi_k = make_sdesc_hi(16, 1024);
+            constexpr uint64_t hi_mn = make_sdesc_hi(L::kBox, 1024);
+
+            mbar_arrive_expect_tx(smem_u32(&bar_a), 2 * L::kTile);
+            for (int b = 0; b < NBOX; b++) {
+                tma_load_3d(a0_s + b * L::kBox, ta0, smem_u32(&bar_a), b * 64, tile * kT, bh);
+                tma_load_3d(a1_s + b * L::kBox, ta1, smem_u32(&bar_a), b * 64, tile * kT, bh);
+            }
+            auto load_step = [&](int t) {
+                const int s = t % kStages;
+                const uint32_t dst = b_s + s * 2 * L::kTile;
+                mbar_arrive_expect_tx(smem_u32(&bar_full[s]), 2 * L::kTile);
+                for (int b = 0; b < NBOX; b++) {
+                    tma_load_3d(dst + b * L::kBox, tb0, smem_u32(&bar_full[s]), b * 64, (first + t) * kT, bh);
+                    tma_load_3d(dst + L::kTile + b * L::kBox, tb1, smem_u32(&bar_full[s]), b * 64, (first + t) * kT, bh);
+                }
+            };
+            for (int t = 0; t < kStages && t < n_steps; t++) load_step(t);
+            bool ok = mbar_wait(smem_u32(&bar_a), 0, ctl, kBwdBarA);
+            for (int t = 0; ok && t < n_steps; t++) {
+                const int s = t % kStages;
+                const uint32_t b0_s = b_s + s * 2 * L::kTile, b1_s = b0_s + L::kTile;
+                if (t >= 1) {
+                    // The products below overwrite the 16-bit operands of step t-1 in TMEM: its
+                    // accumulation MMAs must have completed.  That also frees its stage for step t+1.
+                    if (!mbar_wait(smem_u32(&bar_free[(t - 1) % kStages]), ((t - 1) / kStages) & 1, ctl, kBwdBarFree)) break;
+                    if (t + kStages - 1 < n_steps) load_step(t + kStages - 1);
+                }
+                if (!mbar_wait(smem_u32(&bar_full[s]), (t / kStages) & 1, ctl, kBwdBarFull)) break;
+                tc_fence_after();
+                // T0 = A0 B0^T, T1 = A1 B1^T
+#pragma unroll
+                for (int kk = 0; kk < D / 16; kk++) {
+                    const uint32_t off = (kk >> 2) * L::kBox + (kk & 3) * 32;
+                    mma_f16_ss(tmem + T0_COL, make_sdesc(a0_s + off, hi_k), make_sdesc(b0_s + off, hi_k), idesc_t, kk > 0);
+                }
+#pragma unroll
+                for (int kk = 0; kk < D / 16; kk++) {
+                    const uint32_t off = (kk >> 2) * L::kBox + (kk & 3) * 32;
+                    mma_f16_ss(tmem + T1_COL, make_sdesc(a1_s + off, hi_k), make_sdesc(b1_s + off, hi_k), idesc_t, kk > 0);
+                }
+                tc_commit(smem_u32(&bar_t));
+                if (!mbar_wait(smem_u32(&bar_p), t & 1, ctl, kBwdBarP)) break;
+                tc_fence_after();
+                if (MODE == 0) {
+                    // dV += P^T dO (P^T in T0's first 64 columns), dK += dS^T Q (dS^T in T1's)
+#pragma unroll
+                    for (int kk = 0; kk < kT / 16; kk++)
+                        mma_f16_ts(tmem + ACC0_COL, tmem + T0_COL + kk * 8, make_sdesc(b1_s + kk * 2048, hi_mn),
+                                   idesc_acc, (t > 0 || kk > 0) ? 1u : 0u);
+#pragma unroll
+                    for (int kk = 0; kk < kT / 16; kk++)
+                        mma_f16_ts(tmem + ACC1_COL, tmem + T1_COL + kk * 8, make_sdesc(b0_s + kk * 2048, hi_mn),
+                                   idesc_acc, (t > 0 || kk > 0) ? 1u : 0u);
+                } else {
+                    // dQ += dS K
+#pragma unroll
+                    for (int kk = 0; kk < kT / 16; kk++)
+                        mma_f16_ts(tmem + ACC0_COL, tmem + T1_COL + kk * 8, make_sdesc(b0_s + kk * 2048, hi_mn),
+                                   idesc_acc, (t > 0 || kk > 0) ? 1u : 0u);
+                }
+                tc_commit(smem_u32(&bar_free[s]));
+                if (t == n_steps - 1) tc_commit(smem_u32(&bar_done));
+            }
+        }
+        __syncwarp();
+    } else {
+        // ------------------------------------------------------------ one thread per stationary row
+        const int r = tid;                                  // == TMEM lane: warp * 32 + lane
+        const int r_glob = tile * kT + r;
+        const uint32_t lane_off = static_cast<uint32_t>(warp * 32) << 16;
+        const uint32_t t0 = tmem + lane_off + T0_COL, t1 = tmem + lane_off + T1_COL;
+        const float scale_log2 = scale * kLog2e;
+        const float* lse_h = lse + static_cast<size_t>(bh) * seq_len;
+        const float* delta_h = delta + static_cast<size_t>(bh) * seq_len;
+        // MODE 1: the statistics belong to this thread's query row.  +inf as LSE makes p = 0.
+        float row_lse2 = INFINITY, row_delta = 0.0f;
+        if (MODE == 1 && r_glob < seq_len) { row_lse2 = lse_h[r_glob] * kLog2e; row_delta = delta_h[r_glob]; }
+        bool ok = true;
+        for (int t = 0; ok && t < n_steps; t++) {
+            const int c0 = (first + t) * kT;                // first streamed row (= column of T0/T1) of the step
+            if (MODE == 0) {
+                // statistics of the streamed query tile, one per column; rows past the end get LSE = +inf
+                const int qi = c0 + r;
+                const float l2 = qi < seq_len ? lse_h[qi] * kLog2e : INFINITY;
+                const float dl = qi < seq_len ? delta_h[qi] : 0.0f;
+                named_barrier_sync(1, kT);                  // the previous step's readers are done
+                st_lse[r] = l2;
+                st_delta[r] = dl;
+                named_barrier_sync(1, kT);
+            }
+            if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&bar_t), t & 1, ctl, kBwdBarT))) { ok = false; break; }
+            tc_fence_after();
+#pragma unroll 1
+            for (int c = 0; c < kT / 32; c++) {
+                uint32_t sv[32], dv[32];
+                tmem_ld32_wait(t0 + c * 32, sv);
+                tmem_ld32_wait(t1 + c * 32, dv);
+                uint32_t pk[16], dk[16];
+#pragma unroll
+                for (int e = 0; e < 32; e += 2) {
+                    float p[2], ds[2];
+#pragma unroll
+                    for (int h = 0; h < 2; h++) {
+                        const int col = c * 32 + e + h;
+                        const int cg = c0 + col;            // global index of the streamed row
+                        float l2, dl;
+                        bool valid;
+                        if (MODE == 0) {                    // rows are keys, columns queries
+                            l2 = st_lse[col];
+                            dl = st_delta[col];
+                            valid = !CAUSAL || r_glob <= cg;
+                        } else {                            // rows are queries, columns keys
+                            l2 = row_lse2;
+                            dl = row_delta;
+                            valid = cg < seq_len && (!CAUSAL || cg <= r_glob);
+                        }
+                        const float x = fmaf(__uint_as_float(sv[e + h]), scale_log2, -l2);
+                        p[h] = valid ? ex2_approx(x) : 0.0f;
+                        ds[h] = p[h] * (__uint_as_float(dv[e + h]) - dl) * scale;
+                    }
+                    pk[e >> 1] = pack_16<BF16>(p[0], p[1]);
+                    dk[e >> 1] = pack_16<BF16>(ds[0], ds[1]);
+                }
+                // in place: the 16 columns written here were read by chunk c/2 already
+                if (MODE == 0) tmem_st_x16(t0 + c * 16, pk);
+                tmem_st_x16(t1 + c * 16, dk);
+            }
+            tmem_wait_st();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&bar_p));
+        }
+        // ---- accumulators -> 16-bit -> global
+        if (ok && __all_sync(0xffffffffu, mbar_wait(smem_u32(&bar_done), 0, ctl, kBwdBarDone))) {
+            tc_fence_after();
+#pragma unroll 1
+            for (int which = 0; which < (MODE == 0 ? 2 : 1); which++) {
+                uint16_t* dst = (which == 0 ? out0 : out1) + (static_cast<size_t>(bh) * seq_len + r_glob) * D;
+                const uint32_t acc = tmem + lane_off + (which == 0 ? ACC0_COL : ACC1_COL);
+#pragma unroll 1
+                for (int c = 0; c < D / 32; c++) {
+                    uint32_t a[32];
+                    tmem_ld32_wait(acc + c * 32, a);
+                    if (r_glob < seq_len) {
+#pragma unroll
+                        for (int g8 = 0; g8 < 4; g8++) {
+                            uint4 w;
+                            w.x = pack_16<BF16>(__uint_as_float(a[g8 * 8 + 0]), __uint_as_float(a[g8 * 8 + 1]));
+                            w.y = pack_16<BF16>(__uint_as_float(a[g8 * 8 + 2]), __uint_as_float(a[g8 * 8 + 3]));
+                            w.z = pack_16<BF16>(__uint_as_float(a[g8 * 8 + 4]), __uint_as_float(a[g8 * 8 + 5]));
+                            w.w = pack_16<BF16>(__uint_as_float(a[g8 * 8 + 6]), __uint_as_float(a[g8 * 8 + 7]));
+                            *reinterpret_cast<uint4*>(dst + c * 32 + g8 * 8) = w;
+                        }
+                    }
+                }
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 4) tmem_dealloc(tmem, 512);
+}
+
+template <int D, bool CAUSAL, bool BF16, int MODE>
+int launch_bwd(const fa_backward_args& a, DeviceState* st, const CUtensorMap& tq, const CUtensorMap& tk,
+               const CUtensorMap& tv, const CUtensorMap& tdo, const float* delta, void* out0, void* out1) {
+    using L = BwdSmem<D>;
+    auto kernel = bwd_kernel<D, CAUSAL, BF16, MODE>;
+    static bool configured[64] = {};
+    if (!configured[st->device]) {
+        FA_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
+        configured[st->device] = true;
+    }
+    const int n_tiles = (a.seq_len + kT - 1) / kT;
+    const long long grid = (long long)a.batch_size * a.num_heads * n_tiles;
+    if (grid > 0x7FFFFFFFll) return FA_ERR_INVALID_ARGUMENT;
+    kernel<<<(unsigned)grid, kBwdThreads, L::kTotal, static_cast<cudaStream_t>(a.stream)>>>(
+        tq, tk, tv, tdo, a.lse, delta, static_cast<uint16_t*>(out0), static_cast<uint16_t*>(out1), a.seq_len,
+        n_tiles, a.scale, st->status);
+    FA_CUDA_TRY(cudaGetLastError());
+    return FA_OK;
+}
+
+template <int D, bool CAUSAL, bool BF16>
+int launch_both(const fa_backward_args& a, DeviceState* st, const CUtensorMap& tq, const CUtensorMap& tk,
+                const CUtensorMap& tv, const CUtensorMap& tdo, const float* delta) {
+    int rc = launch_bwd<D, CAUSAL, BF16, 0>(a, st, tq, tk, tv, tdo, delta, a.dv, a.dk);
+    if (rc != FA_OK) return rc;
+    return launch_bwd<D, CAUSAL, BF16, 1>(a, st, tq, tk, tv, tdo, delta, a.dq, nullptr);
+}
+
+}  // namespace
+}  // namespace fa
+
+using namespace fa;
+
+FA_EXPORT size_t fa_backward_workspace_bytes(int batch_size, int num_heads, int seq_len) {
+    if (batch_size <= 0 || num_heads <= 0 || seq_len <= 0) return 0;
+    return (size_t)batch_size * num_heads * seq_len * sizeof(float);
+}
+
+FA_EXPORT int fa_backward(const fa_backward_args* a) {
+    if (!a || !a->q || !a->k || !a->v || !a->o || !a->d_o || !a->lse || !a->dq || !a->dk || !a->dv)
+        return FA_ERR_INVALID_ARGUMENT;
+    if (a->batch_size <= 0 || a->num_heads <= 0 || a->seq_len <= 0) return FA_ERR_INVALID_ARGUMENT;
+    if (!(a->scale > 0.0f) || !std::isfinite(a->scale)) return FA_ERR_INVALID_ARGUMENT;
+    if (a->dtype != FA_DTYPE_F16 && a->dtype != FA_DTYPE_BF16) return FA_ERR_UNSUPPORTED;
+    if (a->d_head != 64 && a->d_head != 128) return FA_ERR_UNSUPPORTED;
+    const void* ptrs[] = {a->q, a->k, a->v, a->o, a->d_o, a->dq, a->dk, a->dv, a->workspace};
+    for (const void* p : ptrs)
+        if (!aligned16(p)) return FA_ERR_MISALIGNED;
+    const size_t need = fa_backward_workspace_bytes(a->batch_size, a->num_heads, a->seq_len);
+    if (!a->workspace || a->workspace_bytes < need) return FA_ERR_WORKSPACE;
+    DeviceState* st = device_state();
+    if (!st) return FA_ERR_CUDA;
+    if (st->cc_major != 10) return FA_ERR_NOT_SM100;
+
+    const uint64_t n_bh = (uint64_t)a->batch_size * a->num_heads;
+    const long long n_rows = (long long)n_bh * a->seq_len;
+    float* delta = static_cast<float*>(a->workspace);
+    cudaStream_t stream = static_cast<cudaStream_t>(a->stream);
+    const bool bf = a->dtype == FA_DTYPE_BF16;
+    {
+        const unsigned blocks = (unsigned)((n_rows + 7) / 8);
+        if (bf) delta_kernel<true><<<blocks, 256, 0, stream>>>(static_cast<const uint16_t*>(a->o),
+                    static_cast<const uint16_t*>(a->d_o), delta, n_rows, a->d_head);
+        else    delta_kernel<false><<<blocks, 256, 0, stream>>>(static_cast<const uint16_t*>(a->o),
+                    static_cast<const uint16_t*>(a->d_o), delta, n_rows, a->d_head);
+        FA_CUDA_TRY(cudaGetLastError());
+    }
+    CUtensorMap tq, tk, tv, tdo;
+    int rc;
+    if ((rc = make_tensor_map_3d(&tq, a->q, a->dtype, a->d_head, a->seq_len, n_bh, 64, kT)) != FA_OK) return rc;
+    if ((rc = make_tensor_map_3d(&tk, a->k, a->dtype, a->d_head, a->seq_len, n_bh, 64, kT)) != FA_OK) return rc;
+    if ((rc = make_tensor_map_3d(&tv, a->v, a->dtype, a->d_head, a->seq_len, n_bh, 64, kT)) != FA_OK) return rc;
+    if ((rc = make_tensor_map_3d(&tdo, a->d_o, a->dtype, a->d_head, a->seq_len, n_bh, 64, kT)) != FA_OK) return rc;
+    const bool causal = a->causal != 0;
+#define FA_BWD(DH)                                                                              \
+    (causal ? (bf ? launch_both<DH, true, true>(*a, st, tq, tk, tv, tdo, delta)                  \
+                  : launch_both<DH, true, false>(*a, st, tq, tk, tv, tdo, delta))                \
+            : (bf ? launch_both<DH, false, true>(*a, st, tq, tk, tv, tdo, delta)                 \
+                  : launch_both<DH, false, false>(*a, st, tq, tk, tv, tdo, delta)))
+    if (a->d_head == 64) return FA_BWD(64);
+    return FA_BWD(128);
+#undef FA_BWD
+}

@@ -221,6 +221,43 @@ typedef struct fa_decode_gqa_args {
 int fa_decode_gqa_default_splits(int batch_size, int num_kv_heads, int seq_len_kv);
 int fa_decode_gqa(const fa_decode_gqa_args* args);
 
+/* ---------------------------------------------------------------------------
+ * fa_backward: dQ, dK, dV of the prefill forward.  No reference counterpart (the
+ * reference is forward only; its kernel stores L "for the backward pass",
+ * kernels/flash_attention.cu:497).  Definition: the gradient of
+ * O = softmax(scale * Q K^T [causal mask]) V (src/demo.cu:28-70) with respect to
+ * Q, K, V for an upstream gradient dO, using the forward's O and LSE:
+ *     P = exp(scale * Q K^T - LSE), dV = P^T dO, dS = P o (dO V^T - delta) * scale,
+ *     delta_i = sum_d dO_id O_id, dQ = dS K, dK = dS^T Q.
+ * All tensors dense [B*H, S, D] in `dtype` (f16 or bf16), lse fp32 [B*H, S]
+ * (natural log, as fa_prefill writes it); d_head 64 or 128.  workspace:
+ * fa_backward_workspace_bytes(B, H, S) bytes of device memory (fp32 delta).
+ * ------------------------------------------------------------------------- */
+typedef struct fa_backward_args {
+    const void*  q;
+    const void*  k;
+    const void*  v;
+    const void*  o;           /* forward output */
+    const void*  d_o;         /* upstream gradient, same layout as o */
+    const float* lse;         /* forward log-sum-exp */
+    void*        dq;
+    void*        dk;
+    void*        dv;
+    int          batch_size;
+    int          num_heads;
+    int          seq_len;
+    int          d_head;
+    float        scale;
+    int          causal;
+    int          dtype;
+    void*        workspace;
+    size_t       workspace_bytes;
+    void*        stream;
+} fa_backward_args;
+
+size_t fa_backward_workspace_bytes(int batch_size, int num_heads, int seq_len);
+int fa_backward(const fa_backward_args* args);
+
 /*
  * LSE merge of n_parts partial results (the exchange step of KV-sequence
  * sharded decode: each rank's (o_f32, lse) gathered into one local buffer).

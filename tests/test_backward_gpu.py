@@ -1,0 +1,69 @@
+"""fa_backward (dQ, dK, dV) against torch autograd evaluated in fp32 on the CPU on the same rounded
+inputs.  The reference project has no backward pass, so there are no golden vectors: the fp32 autograd
+of softmax(scale * Q K^T + mask) V is the definition.  O and LSE fed to the backward come from this
+library's forward.  Tolerance (max abs, relative to the largest reference entry): P and dS are rounded
+to the storage type before the second set of products, so fp16 is held to 4e-3 * max|ref| + 2e-3 and
+bf16 to 3e-2 * max|ref| + 1e-2."""
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+TOL = {"f16": (4e-3, 2e-3), "bf16": (3e-2, 1e-2)}
+TD = {"f16": torch.float16, "bf16": torch.bfloat16}
+
+
+def autograd_reference(q, k, v, d_o, scale, causal):
+    q, k, v = (x.clone().float().requires_grad_(True) for x in (q, k, v))
+    s = (q @ k.transpose(-1, -2)) * scale
+    if causal:
+        n = q.shape[-2]
+        s = s.masked_fill(torch.ones(n, n, dtype=torch.bool).triu(1), float("-inf"))
+    o = torch.softmax(s, -1) @ v
+    o.backward(d_o.float())
+    return q.grad, k.grad, v.grad
+
+
+def run_backward(fa, dev, q, k, v, d_o, scale, causal, dtype):
+    bh, s, d = q.shape
+    dq_, dk_, dv_, ddo = (x.to(dev) for x in (q, k, v, d_o))
+    o = torch.empty_like(dq_)
+    lse = torch.empty((bh, s), device=dev, dtype=torch.float32)
+    fa.prefill(dq_, dk_, dv_, o, lse, 1, bh, s, d, float(scale), causal, dtype=dtype)
+    gq, gk, gv = (torch.full_like(dq_, float("nan")) for _ in range(3))
+    wsb = fa.backward_workspace_bytes(1, bh, s)
+    ws = torch.empty(wsb, device=dev, dtype=torch.uint8)
+    fa.backward(dq_, dk_, dv_, o, ddo, lse, gq, gk, gv, 1, bh, s, d, float(scale), causal, dtype=dtype,
+                workspace=ws, workspace_bytes=wsb)
+    torch.cuda.synchronize()
+    assert fa.device_status() == 0
+    return gq.float().cpu(), gk.float().cpu(), gv.float().cpu()
+
+
+@pytest.mark.parametrize("dtype", ["f16", "bf16"])
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("bh,s,d", [(2, 128, 64), (3, 300, 64), (2, 257, 128), (1, 1024, 128), (2, 40, 64)])
+def test_backward_matches_autograd(fa, dev, dtype, causal, bh, s, d):
+    g = torch.Generator().manual_seed(1000 + s + d)
+    q, k, v, d_o = (torch.randn((bh, s, d), generator=g).to(TD[dtype]) for _ in range(4))
+    scale = 1.0 / np.sqrt(d)
+    ref = autograd_reference(q, k, v, d_o, scale, causal)
+    got = run_backward(fa, dev, q, k, v, d_o, scale, causal, dtype)
+    rel, ab = TOL[dtype]
+    for name, r, x in zip(("dQ", "dK", "dV"), ref, got):
+        assert torch.isfinite(x).all(), name
+        err = (x - r).abs().max().item()
+        assert err < rel * r.abs().max().item() + ab, (name, err, r.abs().max().item())
+
+
+def test_backward_argument_errors(fa, dev):
+    t = torch.zeros(128 * 64, device=dev, dtype=torch.float16)
+    l = torch.zeros(128, device=dev, dtype=torch.float32)
+    ws = torch.empty(1024, device=dev, dtype=torch.uint8)
+    ok = dict(dtype="f16", workspace=ws, workspace_bytes=ws.numel())
+    assert fa.backward_raw(t, t, t, t, t, l, t, t, None, 1, 1, 128, 64, 0.125, False, **ok) == fa.FA_ERR_INVALID_ARGUMENT
+    assert fa.backward_raw(t, t, t, t, t, l, t, t, t, 1, 1, 128, 96, 0.125, False, **ok) == fa.FA_ERR_UNSUPPORTED
+    assert fa.backward_raw(t, t, t, t, t, l, t, t, t, 1, 1, 128, 64, 0.125, False, dtype="f16", workspace=ws,
+                           workspace_bytes=16) == fa.FA_ERR_WORKSPACE
+    assert fa.backward_raw(t, t, t, t, t, l, t, t, t, 1, 1, 128, 64, -1.0, False, **ok) == fa.FA_ERR_INVALID_ARGUMENT
