@@ -488,6 +488,24 @@ def run_other_configs(fa, torch, dev, stream, peaks, gqa_batch=0):
                                             "note": "Q K^T on the 8-bit kind, P V on the 16-bit kind"}
     del q8, k8, v8, o, lse
 
+    # backward pass (dQ, dK, dV) on config 2's shape; 2.5x the forward's FLOP (5 products against 2)
+    bh, s, d = CFG["B"] * CFG["H"], CFG["S"], CFG["D"]
+    sc_b = float(1.0 / np.sqrt(d))
+    qb, kb_, vb, dob = (torch.randn((bh, s, d), device=dev, dtype=torch.float32).to(torch.float16) for _ in range(4))
+    ob = torch.empty_like(qb)
+    lb = torch.empty((bh, s), device=dev, dtype=torch.float32)
+    fa.prefill(qb, kb_, vb, ob, lb, 1, bh, s, d, sc_b, True, dtype="f16", stream=stream)
+    gq, gk, gv = (torch.empty_like(qb) for _ in range(3))
+    wsb = fa.backward_workspace_bytes(1, bh, s)
+    wsbk = torch.empty(wsb, device=dev, dtype=torch.uint8)
+    ms = timed(lambda: fa.backward(qb, kb_, vb, ob, dob, lb, gq, gk, gv, 1, bh, s, d, sc_b, True, dtype="f16",
+                                   workspace=wsbk, workspace_bytes=wsb, stream=stream))
+    tf = 2.5 * causal_flops(bh, s, d) / (ms * 1e-3) / 1e12
+    out[f"backward_f16_b{CFG['B']}_h{CFG['H']}_s{s}_d{d}_causal"] = {
+        "ms": ms, "tflops": tf, "frac_of_measured_bf16_peak": tf / peaks["tflops"],
+        "note": "delta + dK/dV kernel + dQ kernel; FLOP counted as 2.5 x the causal forward"}
+    del qb, kb_, vb, dob, ob, lb, gq, gk, gv
+
     # grouped-query decode over a [B, Skv, Hkv, D] cache: the group's query heads ride in the rows of
     # the tensor-core query tile, K and V stream once per KV head (HBM-bound: report GB/s)
     gb = gqa_batch or 32

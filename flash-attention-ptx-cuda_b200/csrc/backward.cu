@@ -24,9 +24,11 @@
 //                         across CTAs.)
 // Both modes are the same code: two stationary tiles A0, A1, two streamed tiles B0,
 // B1 per step, products T0 = A0 B0^T and T1 = A1 B1^T, accumulators fed from TMEM.
-//   warps 0-3  one thread per stationary row (TMEM lane): exponentials, dS, 16-bit
-//              write-back, final conversion and store of the accumulators.
-//   warp 4     lane 0 issues every TMA load and every tcgen05.mma; the products of
+//   warps 0-7  two threads per stationary row (TMEM lane): warps 0-3 take the first 64
+//              streamed columns of a step, warps 4-7 the other 64: exponentials, dS,
+//              16-bit write-back (each half into the columns it has read itself), final
+//              conversion and store of the accumulators.
+//   warp 8     lane 0 issues every TMA load and every tcgen05.mma; the products of
 //              step t+1 are issued once the accumulations of step t, which read the
 //              same TMEM columns, have completed.
 #include <cmath>
@@ -41,7 +43,8 @@ namespace fa {
 namespace {
 
 constexpr int kT = 128;                  // tile edge: stationary rows per CTA, streamed rows per step
-constexpr int kBwdThreads = 160;
+constexpr int kBwdThreads = 288;
+constexpr int kCtlWarp = 8;
 constexpr int kStages = 2;               // streamed (B0, B1) tile pairs in flight
 constexpr float kLog2e = 1.4426950408889634f;
 
@@ -54,6 +57,11 @@ struct BwdSmem {
     static constexpr int kTile = kNBox * kBox;        // one 128 x D 16-bit tile
     static constexpr int kTotal = 2 * kTile + kStages * 2 * kTile + 1024;
 };
+
+// TMEM column (relative to T0 / T1) of the 16-bit operand slice for streamed rows [16 kk, 16 kk + 16):
+// each half of the compute warps writes its 32 columns of pairs over the start of the 64 fp32
+// columns it reads, so the slices of streamed rows 64-127 start at column 64.
+__host__ __device__ constexpr uint32_t op16_col(int kk) { return (kk < 4 ? 0u : 64u) + (kk & 3) * 8u; }
 
 template <bool BF16>
 __global__ void delta_kernel(const uint16_t* __restrict__ o, const uint16_t* __restrict__ d_o,
@@ -116,19 +124,19 @@ bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         mbar_init(smem_u32(&bar_a), 1);
         for (int i = 0; i < kStages; i++) { mbar_init(smem_u32(&bar_full[i]), 1); mbar_init(smem_u32(&bar_free[i]), 1); }
         mbar_init(smem_u32(&bar_t), 1);
-        mbar_init(smem_u32(&bar_p), 4);                  // one arrival per compute warp
+        mbar_init(smem_u32(&bar_p), 8);                  // one arrival per compute warp
         mbar_init(smem_u32(&bar_done), 1);
         abort_flag = 0;
         fence_mbar_init();
     }
     __syncthreads();
-    if (warp == 4) tmem_alloc(smem_u32(&tmem_slot), 512);
+    if (warp == kCtlWarp) tmem_alloc(smem_u32(&tmem_slot), 512);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = tmem_slot;
 
-    if (warp == 4) {
+    if (warp == kCtlWarp) {
         // ------------------------------------------------------------ TMA + MMA issue (one thread)
         if (lane == 0) {
             const CUtensorMap* ta0 = (MODE == 0) ? &tm_k : &tm_q;
@@ -185,17 +193,17 @@ bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
                     // dV += P^T dO (P^T in T0's first 64 columns), dK += dS^T Q (dS^T in T1's)
 #pragma unroll
                     for (int kk = 0; kk < kT / 16; kk++)
-                        mma_f16_ts(tmem + ACC0_COL, tmem + T0_COL + kk * 8, make_sdesc(b1_s + kk * 2048, hi_mn),
+                        mma_f16_ts(tmem + ACC0_COL, tmem + T0_COL + op16_col(kk), make_sdesc(b1_s + kk * 2048, hi_mn),
                                    idesc_acc, (t > 0 || kk > 0) ? 1u : 0u);
 #pragma unroll
                     for (int kk = 0; kk < kT / 16; kk++)
-                        mma_f16_ts(tmem + ACC1_COL, tmem + T1_COL + kk * 8, make_sdesc(b0_s + kk * 2048, hi_mn),
+                        mma_f16_ts(tmem + ACC1_COL, tmem + T1_COL + op16_col(kk), make_sdesc(b0_s + kk * 2048, hi_mn),
                                    idesc_acc, (t > 0 || kk > 0) ? 1u : 0u);
                 } else {
                     // dQ += dS K
 #pragma unroll
                     for (int kk = 0; kk < kT / 16; kk++)
-                        mma_f16_ts(tmem + ACC0_COL, tmem + T1_COL + kk * 8, make_sdesc(b0_s + kk * 2048, hi_mn),
+                        mma_f16_ts(tmem + ACC0_COL, tmem + T1_COL + op16_col(kk), make_sdesc(b0_s + kk * 2048, hi_mn),
                                    idesc_acc, (t > 0 || kk > 0) ? 1u : 0u);
                 }
                 tc_commit(smem_u32(&bar_free[s]));
@@ -205,9 +213,10 @@ bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         __syncwarp();
     } else {
         // ------------------------------------------------------------ one thread per stationary row
-        const int r = tid;                                  // == TMEM lane: warp * 32 + lane
+        const int r = tid & (kT - 1);                       // == TMEM lane: (warp & 3) * 32 + lane
+        const int half = warp >> 2;                         // which 64 streamed columns of a step
         const int r_glob = tile * kT + r;
-        const uint32_t lane_off = static_cast<uint32_t>(warp * 32) << 16;
+        const uint32_t lane_off = static_cast<uint32_t>((warp & 3) * 32) << 16;
         const uint32_t t0 = tmem + lane_off + T0_COL, t1 = tmem + lane_off + T1_COL;
         const float scale_log2 = scale * kLog2e;
         const float* lse_h = lse + static_cast<size_t>(bh) * seq_len;
@@ -216,25 +225,32 @@ bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         float row_lse2 = INFINITY, row_delta = 0.0f;
         if (MODE == 1 && r_glob < seq_len) { row_lse2 = lse_h[r_glob] * kLog2e; row_delta = delta_h[r_glob]; }
         bool ok = true;
+        // MODE 0: statistics of the streamed query tile, one per column, fetched one step ahead; rows
+        // past the end get LSE = +inf (p = 0)
+        float nx_l2 = INFINITY, nx_dl = 0.0f;
+        if (MODE == 0 && half == 0 && first * kT + r < seq_len) {
+            nx_l2 = lse_h[first * kT + r] * kLog2e;
+            nx_dl = delta_h[first * kT + r];
+        }
         for (int t = 0; ok && t < n_steps; t++) {
             const int c0 = (first + t) * kT;                // first streamed row (= column of T0/T1) of the step
             if (MODE == 0) {
-                // statistics of the streamed query tile, one per column; rows past the end get LSE = +inf
-                const int qi = c0 + r;
-                const float l2 = qi < seq_len ? lse_h[qi] * kLog2e : INFINITY;
-                const float dl = qi < seq_len ? delta_h[qi] : 0.0f;
-                named_barrier_sync(1, kT);                  // the previous step's readers are done
-                st_lse[r] = l2;
-                st_delta[r] = dl;
-                named_barrier_sync(1, kT);
+                named_barrier_sync(1, 2 * kT);              // the previous step's readers are done
+                if (half == 0) { st_lse[r] = nx_l2; st_delta[r] = nx_dl; }
+                named_barrier_sync(1, 2 * kT);
+                const int qn = c0 + kT + r;
+                nx_l2 = INFINITY;
+                nx_dl = 0.0f;
+                if (half == 0 && t + 1 < n_steps && qn < seq_len) { nx_l2 = lse_h[qn] * kLog2e; nx_dl = delta_h[qn]; }
             }
             if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&bar_t), t & 1, ctl, kBwdBarT))) { ok = false; break; }
             tc_fence_after();
 #pragma unroll 1
-            for (int c = 0; c < kT / 32; c++) {
+            for (int c = 2 * half; c < 2 * half + 2; c++) {
                 uint32_t sv[32], dv[32];
-                tmem_ld32_wait(t0 + c * 32, sv);
-                tmem_ld32_wait(t1 + c * 32, dv);
+                tmem_ld_x32(t0 + c * 32, sv);                // both loads in flight, one wait
+                tmem_ld_x32(t1 + c * 32, dv);
+                tmem_ld32_arrive2(sv, dv);
                 uint32_t pk[16], dk[16];
 #pragma unroll
                 for (int e = 0; e < 32; e += 2) {
@@ -261,9 +277,11 @@ bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
                     pk[e >> 1] = pack_16<BF16>(p[0], p[1]);
                     dk[e >> 1] = pack_16<BF16>(ds[0], ds[1]);
                 }
-                // in place: the 16 columns written here were read by chunk c/2 already
-                if (MODE == 0) tmem_st_x16(t0 + c * 16, pk);
-                tmem_st_x16(t1 + c * 16, dk);
+                // in place: the 16 columns written here lie in the 64 this thread reads and were
+                // read by its previous chunk (or this one) already
+                const uint32_t wcol = half * 64 + (c & 1) * 16;
+                if (MODE == 0) tmem_st_x16(t0 + wcol, pk);
+                tmem_st_x16(t1 + wcol, dk);
             }
             tmem_wait_st();
             tc_fence_before();
@@ -278,7 +296,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
                 uint16_t* dst = (which == 0 ? out0 : out1) + (static_cast<size_t>(bh) * seq_len + r_glob) * D;
                 const uint32_t acc = tmem + lane_off + (which == 0 ? ACC0_COL : ACC1_COL);
 #pragma unroll 1
-                for (int c = 0; c < D / 32; c++) {
+                for (int c = half * (D / 64); c < (half + 1) * (D / 64); c++) {
                     uint32_t a[32];
                     tmem_ld32_wait(acc + c * 32, a);
                     if (r_glob < seq_len) {
@@ -299,7 +317,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
 
     tc_fence_before();
     __syncthreads();
-    if (warp == 4) tmem_dealloc(tmem, 512);
+    if (warp == kCtlWarp) tmem_dealloc(tmem, 512);
 }
 
 template <int D, bool CAUSAL, bool BF16, int MODE>

@@ -1,6 +1,8 @@
-"""PyTorch custom operators over the C ABI: ``torch.ops.fa_b200.prefill`` / ``decode``.
+"""PyTorch custom operators over the C ABI: ``torch.ops.fa_b200.prefill`` / ``decode`` /
+``prefill_backward``.
 
-Forward only (the library has no backward pass).  Tensors use the layout of
+``prefill`` is differentiable with respect to q, k and v (``fa_backward``); the gradient of its LSE
+output is not supported.  ``decode`` is forward only.  Tensors use the layout of
 ``torch.nn.functional.scaled_dot_product_attention``: ``[B, H, S, D]``,
 contiguous, fp16 or bf16, on a CUDA device; the kernels see them as the
 reference's ``[B*H, S, D]`` (include/flash_attention.h:46-61).  The operators
@@ -57,6 +59,44 @@ def _(q, k, v, scale, causal):
     return torch.empty_like(q), q.new_empty((b, h, s), dtype=torch.float32)
 
 
+@torch.library.custom_op("fa_b200::prefill_backward", mutates_args=())
+def prefill_backward(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, o: torch.Tensor, lse: torch.Tensor,
+                     d_o: torch.Tensor, scale: float, causal: bool) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Gradients (dQ, dK, dV) of ``prefill`` for the upstream gradient ``d_o`` of O."""
+    _check(q, k, v)
+    b, h, s, d = q.shape
+    q, k, v, o, d_o, lse = (t.contiguous() for t in (q, k, v, o, d_o.to(q.dtype), lse))
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    with torch.cuda.device(q.device):
+        wsb = _fa.backward_workspace_bytes(b, h, s)
+        ws = torch.empty(wsb, device=q.device, dtype=torch.uint8)
+        _fa.backward(q, k, v, o, d_o, lse, dq, dk, dv, b, h, s, d, float(scale), bool(causal),
+                     dtype=_DTYPES[q.dtype], workspace=ws, workspace_bytes=wsb,
+                     stream=torch.cuda.current_stream(q.device))
+    return dq, dk, dv
+
+
+@prefill_backward.register_fake
+def _(q, k, v, o, lse, d_o, scale, causal):
+    return torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+
+
+def _prefill_setup_context(ctx, inputs, output):
+    q, k, v, scale, causal = inputs
+    o, lse = output
+    ctx.save_for_backward(q, k, v, o, lse)
+    ctx.scale, ctx.causal = scale, causal
+
+
+def _prefill_backward(ctx, d_o, d_lse):
+    q, k, v, o, lse = ctx.saved_tensors
+    dq, dk, dv = prefill_backward(q, k, v, o, lse, d_o, ctx.scale, ctx.causal)
+    return dq, dk, dv, None, None
+
+
+torch.library.register_autograd("fa_b200::prefill", _prefill_backward, setup_context=_prefill_setup_context)
+
+
 @torch.library.custom_op("fa_b200::decode", mutates_args=())
 def decode(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float,
            num_splits: int) -> tuple[torch.Tensor, torch.Tensor]:
@@ -104,4 +144,4 @@ def sdpa(query: torch.Tensor, key: torch.Tensor, value: torch.Tensor, attn_mask=
     raise NotImplementedError("fa_b200.sdpa: only self-attention and single-row decode are covered")
 
 
-__all__ = ["prefill", "decode", "sdpa", "FaError"]
+__all__ = ["prefill", "prefill_backward", "decode", "sdpa", "FaError"]

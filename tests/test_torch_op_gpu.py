@@ -49,3 +49,17 @@ def test_non_contiguous_inputs_and_side_stream(op, dev):
         out = op.sdpa(q, q, q)
     st.synchronize()
     assert (out.float().cpu() - ref).abs().max().item() < 2e-3
+
+
+def test_autograd_through_sdpa(op, dev):
+    """loss.backward() through op.sdpa reaches fa_backward; compared with fp32 autograd on the CPU."""
+    g = torch.Generator().manual_seed(8)
+    q, k, v, w = (torch.randn((2, 2, 192, 64), generator=g).half() for _ in range(4))
+    ref_in = [t.float().requires_grad_(True) for t in (q, k, v)]
+    (torch.nn.functional.scaled_dot_product_attention(*ref_in, is_causal=True) * w.float()).sum().backward()
+    dev_in = [t.to(dev).requires_grad_(True) for t in (q, k, v)]
+    (op.sdpa(*dev_in, is_causal=True) * w.to(dev)).sum().backward()
+    for r, x in zip(ref_in, dev_in):
+        assert x.grad is not None and x.grad.dtype == torch.float16
+        err = (x.grad.float().cpu() - r.grad).abs().max().item()
+        assert err < 4e-3 * r.grad.abs().max().item() + 2e-3
