@@ -24,13 +24,18 @@
 //                         across CTAs.)
 // Both modes are the same code: two stationary tiles A0, A1, two streamed tiles B0,
 // B1 per step, products T0 = A0 B0^T and T1 = A1 B1^T, accumulators fed from TMEM.
-//   warps 0-7  two threads per stationary row (TMEM lane): warps 0-3 take the first 64
-//              streamed columns of a step, warps 4-7 the other 64: exponentials, dS,
+// A step streams 64 rows; the products alternate between two TMEM buffers, so the
+// threads work on step t+1 while the accumulating MMAs of step t run.
+//   warps 0-7  two threads per stationary row (TMEM lane): warps 0-3 take the first 32
+//              streamed columns of a step, warps 4-7 the other 32: exponentials, dS,
 //              16-bit write-back (each half into the columns it has read itself), final
 //              conversion and store of the accumulators.
-//   warp 8     lane 0 issues every TMA load and every tcgen05.mma; the products of
-//              step t+1 are issued once the accumulations of step t, which read the
-//              same TMEM columns, have completed.
+//   warp 8     lane 0 issues the TMA loads and the product MMAs; the products of step
+//              t+2 are issued once the accumulations of step t, which read the same
+//              TMEM buffer, have completed.
+//   warp 9     lane 0 issues the accumulating MMAs of a step as soon as its 16-bit
+//              operands are in TMEM (an MMA costs its issuing thread 50-100 clocks, so
+//              the two streams have an issuer each, as in the forward kernel).
 #include <cmath>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
@@ -43,25 +48,49 @@ namespace fa {
 namespace {
 
 constexpr int kT = 128;                  // tile edge: stationary rows per CTA, streamed rows per step
-constexpr int kBwdThreads = 288;
-constexpr int kCtlWarp = 8;
-constexpr int kStages = 2;               // streamed (B0, B1) tile pairs in flight
+constexpr int kBwdThreads = 320;
+constexpr int kCtlWarp = 8;          // TMA loads and the product MMAs
+constexpr int kAccWarp = 9;          // the accumulating MMAs
+constexpr int kW = 64;                   // streamed rows per step (columns of one product)
+constexpr int kStages = 4;               // streamed (B0, B1) tile pairs in flight
 constexpr float kLog2e = 1.4426950408889634f;
 
-enum : int { kBwdBarA = 21, kBwdBarFull = 22, kBwdBarT = 23, kBwdBarP = 24, kBwdBarFree = 25, kBwdBarDone = 26 };
+enum : int { kBwdBarA = 21, kBwdBarFull = 22, kBwdBarT = 23, kBwdBarP = 24, kBwdBarFree = 25, kBwdBarDone = 26, kBwdBarStep = 27 };
+
+// Packed pairs of fp32 (sm_100 has two-wide fp32 FMA/MUL on 64-bit register pairs).
+__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float& lo, float& hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ uint64_t mul2(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
 
 template <int D>
 struct BwdSmem {
     static constexpr int kNBox = D / 64;              // 64-column (128-byte) boxes per row
     static constexpr int kBox = 128 * 128;            // one box: 128 rows x 128 bytes
-    static constexpr int kTile = kNBox * kBox;        // one 128 x D 16-bit tile
-    static constexpr int kTotal = 2 * kTile + kStages * 2 * kTile + 1024;
+    static constexpr int kTile = kNBox * kBox;        // one 128 x D 16-bit tile (stationary operands)
+    static constexpr int kBoxB = kW * 128;            // one box of a streamed tile: kW rows x 128 bytes
+    static constexpr int kTileB = kNBox * kBoxB;      // one kW x D streamed tile
+    static constexpr int kTotal = 2 * kTile + kStages * 2 * kTileB + 1024;
 };
 
-// TMEM column (relative to T0 / T1) of the 16-bit operand slice for streamed rows [16 kk, 16 kk + 16):
-// each half of the compute warps writes its 32 columns of pairs over the start of the 64 fp32
-// columns it reads, so the slices of streamed rows 64-127 start at column 64.
-__host__ __device__ constexpr uint32_t op16_col(int kk) { return (kk < 4 ? 0u : 64u) + (kk & 3) * 8u; }
+// TMEM column (relative to T0 / T1) of the 16-bit operand slice for streamed rows [16 kk, 16 kk + 16)
+// of a step: each half of the compute warps writes its 16 columns of pairs over the start of the 32
+// fp32 columns it reads, so the slices of streamed rows 32-63 start at column 32.
+__host__ __device__ constexpr uint32_t op16_col(int kk) { return (kk < 2 ? 0u : 32u) + (kk & 1) * 8u; }
 
 template <bool BF16>
 __global__ void delta_kernel(const uint16_t* __restrict__ o, const uint16_t* __restrict__ d_o,
@@ -90,21 +119,28 @@ __global__ void delta_kernel(const uint16_t* __restrict__ o, const uint16_t* __r
 }
 
 // MODE 0: dK and dV of one key tile.  MODE 1: dQ of one query tile.
+// ta0 / ta1: maps of the stationary tensors (boxes of 128 rows); tb0 / tb1: maps of the streamed
+// tensors (boxes of kW rows).
 template <int D, bool CAUSAL, bool BF16, int MODE>
 __global__ void __launch_bounds__(kBwdThreads, 1)
-bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-           const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
+bwd_kernel(const __grid_constant__ CUtensorMap ta0, const __grid_constant__ CUtensorMap ta1,
+           const __grid_constant__ CUtensorMap tb0, const __grid_constant__ CUtensorMap tb1,
            const float* __restrict__ lse, const float* __restrict__ delta, uint16_t* __restrict__ out0,
            uint16_t* __restrict__ out1, int seq_len, int n_tiles, float scale, int* status) {
     using L = BwdSmem<D>;
     constexpr int NBOX = L::kNBox;
     constexpr uint32_t FMT = BF16 ? kFmtBF16 : kFmtF16;
-    constexpr uint32_t T0_COL = 0, T1_COL = 128, ACC0_COL = 256, ACC1_COL = 256 + D;
+    // TMEM: two product buffers of 128 columns (T0 in the first kW, T1 in the second kW), then the
+    // accumulators
+    constexpr uint32_t ACC0_COL = 256, ACC1_COL = 256 + D;
     static_assert(ACC1_COL + D <= 512, "TMEM columns");
 
     extern __shared__ uint8_t smem_raw[];
-    __shared__ __align__(8) uint64_t bar_a, bar_full[kStages], bar_free[kStages], bar_t, bar_p, bar_done;
-    __shared__ float st_lse[kT], st_delta[kT];          // MODE 0: statistics of the streamed query tile
+    __shared__ __align__(8) uint64_t bar_a, bar_full[kStages], bar_acc[kStages], bar_t[2], bar_p[2], bar_done;
+    __shared__ __align__(8) uint64_t bar_step;            // MODE 0: rendezvous of the compute warps, once per step
+    // MODE 0: statistics of the streamed queries by step parity, per column pair
+    // {-lse*log2e (col 0, col 1), -delta*scale (col 0, col 1)}: the addends of the two packed FMAs
+    __shared__ __align__(16) float st_neg[2][kW / 2][4];
     __shared__ uint32_t tmem_slot;
     __shared__ int abort_flag;
 
@@ -117,15 +153,19 @@ bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
     const int slot_x = blockIdx.x - bh * n_tiles;
     // heavy tiles first under the causal mask: key tile 0 / the last query tile have the most steps
     const int tile = (MODE == 0) ? slot_x : (n_tiles - 1 - slot_x);
-    const int first = (MODE == 0 && CAUSAL) ? tile : 0;                  // first streamed tile
-    const int n_steps = (MODE == 0) ? (n_tiles - first) : (CAUSAL ? tile + 1 : n_tiles);
+    const int row0 = (MODE == 0 && CAUSAL) ? tile * kT : 0;              // first streamed row
+    const int row_end = (MODE == 1 && CAUSAL) ? min(seq_len, (tile + 1) * kT) : seq_len;
+    const int n_steps = (row_end - row0 + kW - 1) / kW;                 // steps of kW streamed rows
 
     if (tid == 0) {
         mbar_init(smem_u32(&bar_a), 1);
-        for (int i = 0; i < kStages; i++) { mbar_init(smem_u32(&bar_full[i]), 1); mbar_init(smem_u32(&bar_free[i]), 1); }
-        mbar_init(smem_u32(&bar_t), 1);
-        mbar_init(smem_u32(&bar_p), 8);                  // one arrival per compute warp
+        for (int i = 0; i < kStages; i++) { mbar_init(smem_u32(&bar_full[i]), 1); mbar_init(smem_u32(&bar_acc[i]), 1); }
+        for (int i = 0; i < 2; i++) {
+            mbar_init(smem_u32(&bar_t[i]), 1);
+            mbar_init(smem_u32(&bar_p[i]), 8);           // one arrival per compute warp
+        }
         mbar_init(smem_u32(&bar_done), 1);
+        mbar_init(smem_u32(&bar_step), 8);
         abort_flag = 0;
         fence_mbar_init();
     }
@@ -139,154 +179,179 @@ bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
     if (warp == kCtlWarp) {
         // ------------------------------------------------------------ TMA + MMA issue (one thread)
         if (lane == 0) {
-            const CUtensorMap* ta0 = (MODE == 0) ? &tm_k : &tm_q;
-            const CUtensorMap* ta1 = (MODE == 0) ? &tm_v : &tm_do;
-            const CUtensorMap* tb0 = (MODE == 0) ? &tm_q : &tm_k;
-            const CUtensorMap* tb1 = (MODE == 0) ? &tm_do : &tm_v;
-            constexpr uint32_t idesc_t = make_idesc(kT, kT, FMT, FMT, kMajorK, kMajorK);
-            constexpr uint32_t idesc_acc = make_idesc(kT, D, FMT, FMT, kMajorK, kMajorMN);
+            constexpr uint32_t idesc_t = make_idesc(kT, kW, FMT, FMT, kMajorK, kMajorK);
             constexpr uint64_t hi_k = make_sdesc_hi(16, 1024);
-            constexpr uint64_t hi_mn = make_sdesc_hi(L::kBox, 1024);
 
             mbar_arrive_expect_tx(smem_u32(&bar_a), 2 * L::kTile);
             for (int b = 0; b < NBOX; b++) {
-                tma_load_3d(a0_s + b * L::kBox, ta0, smem_u32(&bar_a), b * 64, tile * kT, bh);
-                tma_load_3d(a1_s + b * L::kBox, ta1, smem_u32(&bar_a), b * 64, tile * kT, bh);
+                tma_load_3d(a0_s + b * L::kBox, &ta0, smem_u32(&bar_a), b * 64, tile * kT, bh);
+                tma_load_3d(a1_s + b * L::kBox, &ta1, smem_u32(&bar_a), b * 64, tile * kT, bh);
             }
             auto load_step = [&](int t) {
                 const int s = t % kStages;
-                const uint32_t dst = b_s + s * 2 * L::kTile;
-                mbar_arrive_expect_tx(smem_u32(&bar_full[s]), 2 * L::kTile);
+                const uint32_t dst = b_s + s * 2 * L::kTileB;
+                mbar_arrive_expect_tx(smem_u32(&bar_full[s]), 2 * L::kTileB);
                 for (int b = 0; b < NBOX; b++) {
-                    tma_load_3d(dst + b * L::kBox, tb0, smem_u32(&bar_full[s]), b * 64, (first + t) * kT, bh);
-                    tma_load_3d(dst + L::kTile + b * L::kBox, tb1, smem_u32(&bar_full[s]), b * 64, (first + t) * kT, bh);
+                    tma_load_3d(dst + b * L::kBoxB, &tb0, smem_u32(&bar_full[s]), b * 64, row0 + t * kW, bh);
+                    tma_load_3d(dst + L::kTileB + b * L::kBoxB, &tb1, smem_u32(&bar_full[s]), b * 64, row0 + t * kW, bh);
                 }
+            };
+            // products of step t into buffer t & 1: T0 = A0 B0^T, T1 = A1 B1^T (kW columns each)
+            auto issue_products = [&](int t) -> bool {
+                const int s = t % kStages;
+                const uint32_t b0_s = b_s + s * 2 * L::kTileB, b1_s = b0_s + L::kTileB;
+                const uint32_t tb = tmem + (t & 1) * 128;
+                if (!mbar_wait(smem_u32(&bar_full[s]), (t / kStages) & 1, ctl, kBwdBarFull)) return false;
+                tc_fence_after();
+#pragma unroll
+                for (int kk = 0; kk < D / 16; kk++) {
+                    const uint32_t offa = (kk >> 2) * L::kBox + (kk & 3) * 32, offb = (kk >> 2) * L::kBoxB + (kk & 3) * 32;
+                    mma_f16_ss(tb, make_sdesc(a0_s + offa, hi_k), make_sdesc(b0_s + offb, hi_k), idesc_t, kk > 0);
+                }
+#pragma unroll
+                for (int kk = 0; kk < D / 16; kk++) {
+                    const uint32_t offa = (kk >> 2) * L::kBox + (kk & 3) * 32, offb = (kk >> 2) * L::kBoxB + (kk & 3) * 32;
+                    mma_f16_ss(tb + kW, make_sdesc(a1_s + offa, hi_k), make_sdesc(b1_s + offb, hi_k), idesc_t, kk > 0);
+                }
+                tc_commit(smem_u32(&bar_t[t & 1]));
+                return true;
             };
             for (int t = 0; t < kStages && t < n_steps; t++) load_step(t);
             bool ok = mbar_wait(smem_u32(&bar_a), 0, ctl, kBwdBarA);
             for (int t = 0; ok && t < n_steps; t++) {
+                if (t >= 2) {
+                    // the products of step t reuse the TMEM buffer of step t-2, and step t-2+kStages its
+                    // shared-memory stage: the accumulations of step t-2 must have completed
+                    if (!mbar_wait(smem_u32(&bar_acc[(t - 2) % kStages]), ((t - 2) / kStages) & 1, ctl, kBwdBarFree)) break;
+                    if (t - 2 + kStages < n_steps) load_step(t - 2 + kStages);
+                }
+                ok = issue_products(t);
+            }
+        }
+        __syncwarp();
+    } else if (warp == kAccWarp) {
+        // ------------------------------------------------------------ accumulating MMAs (one thread)
+        if (lane == 0) {
+            constexpr uint32_t idesc_acc = make_idesc(kT, D, FMT, FMT, kMajorK, kMajorMN);
+            constexpr uint64_t hi_mn = make_sdesc_hi(L::kBoxB, 1024);
+            for (int t = 0; t < n_steps; t++) {
                 const int s = t % kStages;
-                const uint32_t b0_s = b_s + s * 2 * L::kTile, b1_s = b0_s + L::kTile;
-                if (t >= 1) {
-                    // The products below overwrite the 16-bit operands of step t-1 in TMEM: its
-                    // accumulation MMAs must have completed.  That also frees its stage for step t+1.
-                    if (!mbar_wait(smem_u32(&bar_free[(t - 1) % kStages]), ((t - 1) / kStages) & 1, ctl, kBwdBarFree)) break;
-                    if (t + kStages - 1 < n_steps) load_step(t + kStages - 1);
-                }
-                if (!mbar_wait(smem_u32(&bar_full[s]), (t / kStages) & 1, ctl, kBwdBarFull)) break;
-                tc_fence_after();
-                // T0 = A0 B0^T, T1 = A1 B1^T
-#pragma unroll
-                for (int kk = 0; kk < D / 16; kk++) {
-                    const uint32_t off = (kk >> 2) * L::kBox + (kk & 3) * 32;
-                    mma_f16_ss(tmem + T0_COL, make_sdesc(a0_s + off, hi_k), make_sdesc(b0_s + off, hi_k), idesc_t, kk > 0);
-                }
-#pragma unroll
-                for (int kk = 0; kk < D / 16; kk++) {
-                    const uint32_t off = (kk >> 2) * L::kBox + (kk & 3) * 32;
-                    mma_f16_ss(tmem + T1_COL, make_sdesc(a1_s + off, hi_k), make_sdesc(b1_s + off, hi_k), idesc_t, kk > 0);
-                }
-                tc_commit(smem_u32(&bar_t));
-                if (!mbar_wait(smem_u32(&bar_p), t & 1, ctl, kBwdBarP)) break;
+                const uint32_t b0_s = b_s + s * 2 * L::kTileB, b1_s = b0_s + L::kTileB;
+                const uint32_t tb = tmem + (t & 1) * 128;
+                if (!mbar_wait(smem_u32(&bar_p[t & 1]), (t >> 1) & 1, ctl, kBwdBarP)) break;
                 tc_fence_after();
                 if (MODE == 0) {
-                    // dV += P^T dO (P^T in T0's first 64 columns), dK += dS^T Q (dS^T in T1's)
+                    // dV += P^T dO (P^T over T0), dK += dS^T Q (dS^T over T1)
 #pragma unroll
-                    for (int kk = 0; kk < kT / 16; kk++)
-                        mma_f16_ts(tmem + ACC0_COL, tmem + T0_COL + op16_col(kk), make_sdesc(b1_s + kk * 2048, hi_mn),
+                    for (int kk = 0; kk < kW / 16; kk++)
+                        mma_f16_ts(tmem + ACC0_COL, tb + op16_col(kk), make_sdesc(b1_s + kk * 2048, hi_mn),
                                    idesc_acc, (t > 0 || kk > 0) ? 1u : 0u);
 #pragma unroll
-                    for (int kk = 0; kk < kT / 16; kk++)
-                        mma_f16_ts(tmem + ACC1_COL, tmem + T1_COL + op16_col(kk), make_sdesc(b0_s + kk * 2048, hi_mn),
+                    for (int kk = 0; kk < kW / 16; kk++)
+                        mma_f16_ts(tmem + ACC1_COL, tb + kW + op16_col(kk), make_sdesc(b0_s + kk * 2048, hi_mn),
                                    idesc_acc, (t > 0 || kk > 0) ? 1u : 0u);
                 } else {
                     // dQ += dS K
 #pragma unroll
-                    for (int kk = 0; kk < kT / 16; kk++)
-                        mma_f16_ts(tmem + ACC0_COL, tmem + T1_COL + op16_col(kk), make_sdesc(b0_s + kk * 2048, hi_mn),
+                    for (int kk = 0; kk < kW / 16; kk++)
+                        mma_f16_ts(tmem + ACC0_COL, tb + kW + op16_col(kk), make_sdesc(b0_s + kk * 2048, hi_mn),
                                    idesc_acc, (t > 0 || kk > 0) ? 1u : 0u);
                 }
-                tc_commit(smem_u32(&bar_free[s]));
+                tc_commit(smem_u32(&bar_acc[s]));
                 if (t == n_steps - 1) tc_commit(smem_u32(&bar_done));
             }
         }
         __syncwarp();
     } else {
-        // ------------------------------------------------------------ one thread per stationary row
+        // ------------------------------------------------------------ two threads per stationary row
         const int r = tid & (kT - 1);                       // == TMEM lane: (warp & 3) * 32 + lane
-        const int half = warp >> 2;                         // which 64 streamed columns of a step
+        const int half = warp >> 2;                         // which 32 streamed columns of a step
         const int r_glob = tile * kT + r;
         const uint32_t lane_off = static_cast<uint32_t>((warp & 3) * 32) << 16;
-        const uint32_t t0 = tmem + lane_off + T0_COL, t1 = tmem + lane_off + T1_COL;
         const float scale_log2 = scale * kLog2e;
         const float* lse_h = lse + static_cast<size_t>(bh) * seq_len;
         const float* delta_h = delta + static_cast<size_t>(bh) * seq_len;
         // MODE 1: the statistics belong to this thread's query row.  +inf as LSE makes p = 0.
         float row_lse2 = INFINITY, row_delta = 0.0f;
         if (MODE == 1 && r_glob < seq_len) { row_lse2 = lse_h[r_glob] * kLog2e; row_delta = delta_h[r_glob]; }
-        bool ok = true;
-        // MODE 0: statistics of the streamed query tile, one per column, fetched one step ahead; rows
-        // past the end get LSE = +inf (p = 0)
-        float nx_l2 = INFINITY, nx_dl = 0.0f;
-        if (MODE == 0 && half == 0 && first * kT + r < seq_len) {
-            nx_l2 = lse_h[first * kT + r] * kLog2e;
-            nx_dl = delta_h[first * kT + r];
+        // MODE 0: statistics of the streamed queries, one per column, staged in shared memory one step
+        // ahead by threads 0..kW-1 and fetched from global memory two steps ahead; rows past the end
+        // get LSE = +inf (p = 0)
+        auto fetch_stats = [&](int t, float& l2, float& dl) {
+            const int qi = row0 + t * kW + tid;
+            l2 = INFINITY;
+            dl = 0.0f;
+            if (MODE == 0 && tid < kW && t < n_steps && qi < seq_len) { l2 = lse_h[qi] * kLog2e; dl = delta_h[qi]; }
+        };
+        float nx_l2, nx_dl;
+        if (MODE == 0) {
+            fetch_stats(0, nx_l2, nx_dl);
+            if (tid < kW) { st_neg[0][tid >> 1][tid & 1] = -nx_l2; st_neg[0][tid >> 1][2 + (tid & 1)] = -nx_dl * scale; }
+            fetch_stats(1, nx_l2, nx_dl);
         }
+        bool ok = true;
         for (int t = 0; ok && t < n_steps; t++) {
-            const int c0 = (first + t) * kT;                // first streamed row (= column of T0/T1) of the step
+            const int c0 = row0 + t * kW;                   // first streamed row (= column of T0/T1) of the step
+            const uint32_t tb = tmem + lane_off + (t & 1) * 128;
             if (MODE == 0) {
-                named_barrier_sync(1, 2 * kT);              // the previous step's readers are done
-                if (half == 0) { st_lse[r] = nx_l2; st_delta[r] = nx_dl; }
-                named_barrier_sync(1, 2 * kT);
-                const int qn = c0 + kT + r;
-                nx_l2 = INFINITY;
-                nx_dl = 0.0f;
-                if (half == 0 && t + 1 < n_steps && qn < seq_len) { nx_l2 = lse_h[qn] * kLog2e; nx_dl = delta_h[qn]; }
-            }
-            if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&bar_t), t & 1, ctl, kBwdBarT))) { ok = false; break; }
-            tc_fence_after();
-#pragma unroll 1
-            for (int c = 2 * half; c < 2 * half + 2; c++) {
-                uint32_t sv[32], dv[32];
-                tmem_ld_x32(t0 + c * 32, sv);                // both loads in flight, one wait
-                tmem_ld_x32(t1 + c * 32, dv);
-                tmem_ld32_arrive2(sv, dv);
-                uint32_t pk[16], dk[16];
-#pragma unroll
-                for (int e = 0; e < 32; e += 2) {
-                    float p[2], ds[2];
-#pragma unroll
-                    for (int h = 0; h < 2; h++) {
-                        const int col = c * 32 + e + h;
-                        const int cg = c0 + col;            // global index of the streamed row
-                        float l2, dl;
-                        bool valid;
-                        if (MODE == 0) {                    // rows are keys, columns queries
-                            l2 = st_lse[col];
-                            dl = st_delta[col];
-                            valid = !CAUSAL || r_glob <= cg;
-                        } else {                            // rows are queries, columns keys
-                            l2 = row_lse2;
-                            dl = row_delta;
-                            valid = cg < seq_len && (!CAUSAL || cg <= r_glob);
-                        }
-                        const float x = fmaf(__uint_as_float(sv[e + h]), scale_log2, -l2);
-                        p[h] = valid ? ex2_approx(x) : 0.0f;
-                        ds[h] = p[h] * (__uint_as_float(dv[e + h]) - dl) * scale;
-                    }
-                    pk[e >> 1] = pack_16<BF16>(p[0], p[1]);
-                    dk[e >> 1] = pack_16<BF16>(ds[0], ds[1]);
+                // step t-1's readers are past their reads of the other parity; this step's values
+                // (written a step ago) become visible
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&bar_step));
+                if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&bar_step), t & 1, ctl, kBwdBarStep))) { ok = false; break; }
+                if (tid < kW) {
+                    st_neg[(t + 1) & 1][tid >> 1][tid & 1] = -nx_l2;
+                    st_neg[(t + 1) & 1][tid >> 1][2 + (tid & 1)] = -nx_dl * scale;
                 }
-                // in place: the 16 columns written here lie in the 64 this thread reads and were
-                // read by its previous chunk (or this one) already
-                const uint32_t wcol = half * 64 + (c & 1) * 16;
-                if (MODE == 0) tmem_st_x16(t0 + wcol, pk);
-                tmem_st_x16(t1 + wcol, dk);
+                fetch_stats(t + 2, nx_l2, nx_dl);
             }
+            if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&bar_t[t & 1]), (t >> 1) & 1, ctl, kBwdBarT))) { ok = false; break; }
+            tc_fence_after();
+            uint32_t sv[32], dv[32];
+            tmem_ld_x32(tb + half * 32, sv);                // both loads in flight, one wait
+            tmem_ld_x32(tb + kW + half * 32, dv);
+            tmem_ld32_arrive2(sv, dv);
+            // masking only where the step touches the causal diagonal or the ragged end: masked
+            // scores become -inf, so p = 0 and dS = 0
+            const bool need_mask = (MODE == 0) ? (CAUSAL && c0 < (tile + 1) * kT)
+                                               : ((CAUSAL && c0 + kW > tile * kT) || c0 + kW > seq_len);
+            if (need_mask) {
+#pragma unroll
+                for (int e = 0; e < 32; e++) {
+                    const int cg = c0 + half * 32 + e;      // global index of the streamed row
+                    const bool valid = (MODE == 0) ? (r_glob <= cg) : (cg < seq_len && (!CAUSAL || cg <= r_glob));
+                    sv[e] = valid ? sv[e] : 0xff800000u;    // -inf
+                }
+            }
+            uint32_t pk[16], dk[16];
+            const uint64_t scale_log2_2 = pack2(scale_log2, scale_log2), scale2 = pack2(scale, scale);
+            const uint64_t row_neg_l2 = pack2(-row_lse2, -row_lse2), row_neg_dl = pack2(-row_delta * scale, -row_delta * scale);
+#pragma unroll
+            for (int e = 0; e < 32; e += 2) {
+                uint64_t neg_l2 = row_neg_l2, neg_dl = row_neg_dl;
+                if (MODE == 0) {                            // per column: one 16-byte shared load per pair
+                    const float4 st = *reinterpret_cast<const float4*>(st_neg[t & 1][half * 16 + (e >> 1)]);
+                    neg_l2 = pack2(st.x, st.y);
+                    neg_dl = pack2(st.z, st.w);
+                }
+                // p = 2^(s * scale * log2e - lse * log2e);  dS = p * (dP * scale - delta * scale)
+                const uint64_t x = fma2(pack2(__uint_as_float(sv[e]), __uint_as_float(sv[e + 1])), scale_log2_2, neg_l2);
+                float x0, x1;
+                unpack2(x, x0, x1);
+                const float p0 = ex2_approx(x0), p1 = ex2_approx(x1);
+                const uint64_t g = fma2(pack2(__uint_as_float(dv[e]), __uint_as_float(dv[e + 1])), scale2, neg_dl);
+                float d0, d1;
+                unpack2(mul2(pack2(p0, p1), g), d0, d1);
+                pk[e >> 1] = pack_16<BF16>(p0, p1);
+                dk[e >> 1] = pack_16<BF16>(d0, d1);
+            }
+            // in place: the 16 columns written here are the first half of the 32 this thread has read
+            if (MODE == 0) tmem_st_x16(tb + half * 32, pk);
+            tmem_st_x16(tb + kW + half * 32, dk);
             tmem_wait_st();
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(&bar_p));
+            if (lane == 0) mbar_arrive(smem_u32(&bar_p[t & 1]));
         }
         // ---- accumulators -> 16-bit -> global
         if (ok && __all_sync(0xffffffffu, mbar_wait(smem_u32(&bar_done), 0, ctl, kBwdBarDone))) {
@@ -340,12 +405,14 @@ int launch_bwd(const fa_backward_args& a, DeviceState* st, const CUtensorMap& tq
     return FA_OK;
 }
 
+// maps[0..3]: q, k, v, dO with boxes of 128 rows; maps[4..7]: the same with boxes of kW rows
 template <int D, bool CAUSAL, bool BF16>
-int launch_both(const fa_backward_args& a, DeviceState* st, const CUtensorMap& tq, const CUtensorMap& tk,
-                const CUtensorMap& tv, const CUtensorMap& tdo, const float* delta) {
-    int rc = launch_bwd<D, CAUSAL, BF16, 0>(a, st, tq, tk, tv, tdo, delta, a.dv, a.dk);
+int launch_both(const fa_backward_args& a, DeviceState* st, const CUtensorMap* m, const float* delta) {
+    // dK, dV: K and V stay (128-row boxes), Q and dO stream (kW-row boxes)
+    int rc = launch_bwd<D, CAUSAL, BF16, 0>(a, st, m[1], m[2], m[4], m[7], delta, a.dv, a.dk);
     if (rc != FA_OK) return rc;
-    return launch_bwd<D, CAUSAL, BF16, 1>(a, st, tq, tk, tv, tdo, delta, a.dq, nullptr);
+    // dQ: Q and dO stay, K and V stream
+    return launch_bwd<D, CAUSAL, BF16, 1>(a, st, m[0], m[3], m[5], m[6], delta, a.dq, nullptr);
 }
 
 }  // namespace
@@ -387,18 +454,19 @@ FA_EXPORT int fa_backward(const fa_backward_args* a) {
                     static_cast<const uint16_t*>(a->d_o), delta, n_rows, a->d_head);
         FA_CUDA_TRY(cudaGetLastError());
     }
-    CUtensorMap tq, tk, tv, tdo;
+    CUtensorMap maps[8];
+    const void* tensors[4] = {a->q, a->k, a->v, a->d_o};
     int rc;
-    if ((rc = make_tensor_map_3d(&tq, a->q, a->dtype, a->d_head, a->seq_len, n_bh, 64, kT)) != FA_OK) return rc;
-    if ((rc = make_tensor_map_3d(&tk, a->k, a->dtype, a->d_head, a->seq_len, n_bh, 64, kT)) != FA_OK) return rc;
-    if ((rc = make_tensor_map_3d(&tv, a->v, a->dtype, a->d_head, a->seq_len, n_bh, 64, kT)) != FA_OK) return rc;
-    if ((rc = make_tensor_map_3d(&tdo, a->d_o, a->dtype, a->d_head, a->seq_len, n_bh, 64, kT)) != FA_OK) return rc;
+    for (int i = 0; i < 4; i++) {
+        if ((rc = make_tensor_map_3d(&maps[i], tensors[i], a->dtype, a->d_head, a->seq_len, n_bh, 64, kT)) != FA_OK) return rc;
+        if ((rc = make_tensor_map_3d(&maps[4 + i], tensors[i], a->dtype, a->d_head, a->seq_len, n_bh, 64, kW)) != FA_OK) return rc;
+    }
     const bool causal = a->causal != 0;
 #define FA_BWD(DH)                                                                              \
-    (causal ? (bf ? launch_both<DH, true, true>(*a, st, tq, tk, tv, tdo, delta)                  \
-                  : launch_both<DH, true, false>(*a, st, tq, tk, tv, tdo, delta))                \
-            : (bf ? launch_both<DH, false, true>(*a, st, tq, tk, tv, tdo, delta)                 \
-                  : launch_both<DH, false, false>(*a, st, tq, tk, tv, tdo, delta)))
+    (causal ? (bf ? launch_both<DH, true, true>(*a, st, maps, delta)                             \
+                  : launch_both<DH, true, false>(*a, st, maps, delta))                           \
+            : (bf ? launch_both<DH, false, true>(*a, st, maps, delta)                            \
+                  : launch_both<DH, false, false>(*a, st, maps, delta)))
     if (a->d_head == 64) return FA_BWD(64);
     return FA_BWD(128);
 #undef FA_BWD
