@@ -107,3 +107,82 @@ def test_config4_decode_b32_h32_skv16384_d128_every_head(fa, dev, oracle):
         worst_o = max(worst_o, float(np.abs(og[i:i + 128] - o_ref[:, 0]).max()))
         worst_l = max(worst_l, float(np.abs(lg[i:i + 128] - l_ref[:, 0]).max()))
     assert worst_o < 2e-3 and worst_l < 1e-3, (worst_o, worst_l)
+
+
+def test_backward_config2_shape_full_size(fa, dev):
+    """fa_backward on config 2's shape (fp16 B=8 H=12 S=2048 D=64 causal).  (a) three heads against
+    fp32 autograd run on the GPU by torch (reference of the same op; tolerance as in
+    test_backward_gpu: 4e-3 * max|ref| + 2e-3); (b) linearity in dO over the whole tensor:
+    backward(2 dO) == 2 backward(dO) exactly up to fp16 rounding of the outputs; (c) all finite."""
+    import torch
+    bh, s, d = 96, 2048, 64
+    scale = float(1.0 / np.sqrt(np.float32(d)))
+    q, k, v, d_o = (_gpu_normal(torch, dev, 7000 + i, (bh, s, d), torch.float16) for i in range(4))
+    o = torch.empty_like(q)
+    lse = torch.empty((bh, s), device=dev, dtype=torch.float32)
+    fa.prefill(q, k, v, o, lse, 8, 12, s, d, scale, True, dtype="f16")
+    wsb = fa.backward_workspace_bytes(8, 12, s)
+    ws = torch.empty(wsb, device=dev, dtype=torch.uint8)
+
+    def bwd(go):
+        g = [torch.full_like(q, float("nan")) for _ in range(3)]
+        fa.backward(q, k, v, o, go, lse, g[0], g[1], g[2], 8, 12, s, d, scale, True, dtype="f16",
+                    workspace=ws, workspace_bytes=wsb)
+        torch.cuda.synchronize()
+        return g
+
+    g1 = bwd(d_o)
+    assert fa.device_status() == 0
+    for t in g1:
+        assert torch.isfinite(t.float()).all()
+    heads = [0, 41, 95]
+    qr, kr, vr = (x[heads].float().requires_grad_(True) for x in (q, k, v))
+    sc = (qr @ kr.transpose(-1, -2)) * scale
+    sc = sc.masked_fill(torch.ones(s, s, dtype=torch.bool, device=dev).triu(1), float("-inf"))
+    (torch.softmax(sc, -1) @ vr).backward(d_o[heads].float())
+    for name, ref, got in zip(("dQ", "dK", "dV"), (qr.grad, kr.grad, vr.grad), g1):
+        err = (got[heads].float() - ref).abs().max().item()
+        assert err < 4e-3 * ref.abs().max().item() + 2e-3, (name, err)
+    g2 = bwd((d_o.float() * 2).half())
+    for a, b in zip(g1, g2):
+        # doubling dO doubles every intermediate exactly (powers of two), so only the final
+        # rounding can differ, and 2x a representable fp16 value is representable
+        assert (b.float() - 2 * a.float()).abs().max().item() < 1e-3 * a.float().abs().max().item() + 1e-6
+
+
+def test_gqa_decode_full_size_split_invariance(fa, dev):
+    """Grouped-query decode at B=32 Hq=32 Hkv=8 Skv=16384 D=128 on a [B, Skv, Hkv, D] cache: the result
+    must not depend on the number of KV splits (1 vs the default), and one sequence is checked against
+    fa_decode (the streaming kernel) on the same keys with the KV heads repeated."""
+    import torch
+    b, hq, hkv, skv, d = 32, 32, 8, 16384, 128
+    scale = float(1.0 / np.sqrt(np.float32(d)))
+    kc, vc = (_gpu_normal(torch, dev, 7100 + i, (b, skv, hkv, d), torch.float16) for i in range(2))
+    q = _gpu_normal(torch, dev, 7102, (b, hq, d), torch.float16)
+    strides = (skv * hkv * d, d, hkv * d)
+    outs = []
+    for splits in (0, 1):
+        n = splits or fa.decode_gqa_default_splits(b, hkv, skv)
+        wsb = fa.decode_workspace_bytes(b, hq, d, n)
+        ws = torch.empty(wsb, device=dev, dtype=torch.uint8)
+        o = torch.full((b, hq, d), float("nan"), device=dev, dtype=torch.float16)
+        l = torch.full((b, hq), float("nan"), device=dev, dtype=torch.float32)
+        fa.decode_gqa(q, kc, vc, o, l, b, hq, hkv, skv, d, scale, dtype="f16", num_splits=splits,
+                      kv_strides=strides, workspace=ws, workspace_bytes=wsb)
+        torch.cuda.synchronize()
+        assert fa.device_status() == 0
+        outs.append((o, l))
+    assert (outs[0][0].float() - outs[1][0].float()).abs().max().item() < 2e-3
+    assert (outs[0][1] - outs[1][1]).abs().max().item() < 1e-3
+    # sequence 5 through the streaming decode kernel with its KV heads expanded to 32
+    kx = kc[5].permute(1, 0, 2).repeat_interleave(hq // hkv, dim=0).contiguous()     # [Hq, Skv, D]
+    vx = vc[5].permute(1, 0, 2).repeat_interleave(hq // hkv, dim=0).contiguous()
+    o2 = torch.empty((hq, d), device=dev, dtype=torch.float16)
+    l2 = torch.empty((hq,), device=dev, dtype=torch.float32)
+    wsb = fa.decode_workspace_bytes(1, hq, d, 16)
+    ws = torch.empty(wsb, device=dev, dtype=torch.uint8)
+    fa.decode(q[5].contiguous(), kx, vx, o2, l2, None, 1, hq, skv, d, scale, dtype="f16", num_splits=16,
+              workspace=ws, workspace_bytes=wsb)
+    torch.cuda.synchronize()
+    assert (o2.float() - outs[0][0][5].float()).abs().max().item() < 2e-3
+    assert (l2 - outs[0][1][5]).abs().max().item() < 1e-3
