@@ -341,7 +341,6 @@ def run_b200_arm(args, rank, local_rank, world):
     e2e_val = world * flops_step / e2e_s / 1e12
     h2d = 3 * bh * S * D * 2
     d2h = bh * S * D * 2 + bh * S * 4
-    status = fa.device_status()
 
     # ---- decode HBM roofline (rank-local; reported from rank 0)
     decode = None
@@ -358,6 +357,7 @@ def run_b200_arm(args, rank, local_rank, world):
     if not args.no_extra:
         other = run_other_configs(fa, torch, dev, stream, peaks, args.gqa_batch)
 
+    status = fa.device_status()              # after every kernel of this run
     clocks = sampler.summary()
     cpu_baseline = None
     if rank == 0 and world == 1 and not args.no_cpu:

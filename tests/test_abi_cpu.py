@@ -45,3 +45,28 @@ def test_host_side_validation_needs_no_device(fa):
     assert lib.fa_decode(None) == fa.FA_ERR_INVALID_ARGUMENT
     assert fa.decode_workspace_bytes(32, 32, 128, 16) == 32 * 32 * 16 * 129 * 4
     assert fa.decode_workspace_bytes(0, 1, 128, 1) == 0
+
+
+def test_host_side_validation_of_the_added_entry_points(fa):
+    lib = fa.lib()
+    assert lib.fa_decode_gqa(None) == fa.FA_ERR_INVALID_ARGUMENT
+    assert lib.fa_backward(None) == fa.FA_ERR_INVALID_ARGUMENT
+    g = fa.DecodeGqaArgs(q=16, k=16, v=16, o=16, batch_size=1, num_q_heads=6, num_kv_heads=4, seq_len_kv=128,
+                         d_head=64, scale=0.125, dtype=0)
+    assert lib.fa_decode_gqa(ctypes.byref(g)) == fa.FA_ERR_INVALID_ARGUMENT   # 6 query heads over 4 KV heads
+    g.num_q_heads = 8
+    g.d_head = 96
+    assert lib.fa_decode_gqa(ctypes.byref(g)) == fa.FA_ERR_UNSUPPORTED
+    g.d_head = 64
+    g.kv_batch_stride, g.kv_head_stride, g.kv_row_stride = 8192, 4100, 64    # head stride not a multiple of 8
+    assert lib.fa_decode_gqa(ctypes.byref(g)) == fa.FA_ERR_MISALIGNED
+    g.kv_head_stride = 4096
+    g.block_table, g.page_size, g.num_pages, g.block_table_stride, g.kv_page_stride = 16, 24, 4, 8, 4096
+    assert lib.fa_decode_gqa(ctypes.byref(g)) == fa.FA_ERR_INVALID_ARGUMENT   # page size not a power of two
+    b = fa.BackwardArgs(q=16, k=16, v=16, o=16, d_o=16, lse=16, dq=16, dk=16, dv=16, batch_size=1, num_heads=1,
+                        seq_len=128, d_head=64, scale=0.125, causal=1, dtype=2)
+    assert lib.fa_backward(ctypes.byref(b)) == fa.FA_ERR_UNSUPPORTED          # e4m3 has no backward
+    b.dtype = 0
+    b.workspace, b.workspace_bytes = 16, 8
+    assert lib.fa_backward(ctypes.byref(b)) == fa.FA_ERR_WORKSPACE
+    assert fa.backward_workspace_bytes(2, 3, 100) == 2 * 3 * 100 * 4
