@@ -157,6 +157,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap ta0, const __grid_constant__ CUte
     const int row_end = (MODE == 1 && CAUSAL) ? min(seq_len, (tile + 1) * kT) : seq_len;
     const int n_steps = (row_end - row0 + kW - 1) / kW;                 // steps of kW streamed rows
 
+    if (MODE == 0 && tid == 0) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     if (tid == 0) {
         mbar_init(smem_u32(&bar_a), 1);
         for (int i = 0; i < kStages; i++) { mbar_init(smem_u32(&bar_full[i]), 1); mbar_init(smem_u32(&bar_acc[i]), 1); }
@@ -398,10 +399,22 @@ int launch_bwd(const fa_backward_args& a, DeviceState* st, const CUtensorMap& tq
     const int n_tiles = (a.seq_len + kT - 1) / kT;
     const long long grid = (long long)a.batch_size * a.num_heads * n_tiles;
     if (grid > 0x7FFFFFFFll) return FA_ERR_INVALID_ARGUMENT;
-    kernel<<<(unsigned)grid, kBwdThreads, L::kTotal, static_cast<cudaStream_t>(a.stream)>>>(
-        tq, tk, tv, tdo, a.lse, delta, static_cast<uint16_t*>(out0), static_cast<uint16_t*>(out1), a.seq_len,
-        n_tiles, a.scale, st->status);
-    FA_CUDA_TRY(cudaGetLastError());
+    // The dQ kernel (MODE 1) reads nothing the dK/dV kernel (MODE 0) writes, so it is launched as a
+    // programmatic dependent: its CTAs may start on SMs the first kernel no longer needs (that kernel
+    // signals at its start), instead of waiting for its last CTA.  delta comes from a kernel that
+    // completed before MODE 0 started.
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3(kBwdThreads);
+    cfg.dynamicSmemBytes = L::kTotal;
+    cfg.stream = static_cast<cudaStream_t>(a.stream);
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = (MODE == 1) ? 1 : 0;
+    FA_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, tq, tk, tv, tdo, a.lse, delta, static_cast<uint16_t*>(out0),
+                                   static_cast<uint16_t*>(out1), a.seq_len, n_tiles, a.scale, st->status));
     return FA_OK;
 }
 
