@@ -528,6 +528,27 @@ def run_other_configs(fa, torch, dev, stream, peaks, gqa_batch=0):
             "ms": ms, "GBps": gbs, "frac_of_measured_hbm_peak": gbs / peaks["hbm_gbs"], "splits": splits,
             "algorithmic_bytes": algo, "tokens_per_s": b / (ms * 1e-3)}
         del kc, vc, ws
+
+    # the same decode over an e4m3 cache (one byte per element; Q e4m3 as well, per-(batch, KV head) scales)
+    b, hq, hkv, skv, d = gb, 32, 8, 16384, 128
+    kc8 = torch.randn((b, skv, hkv, d), device=dev, dtype=torch.float32).to(torch.float8_e4m3fn).view(torch.uint8)
+    vc8 = torch.randn((b, skv, hkv, d), device=dev, dtype=torch.float32).to(torch.float8_e4m3fn).view(torch.uint8)
+    q8g = torch.randn((b, hq, d), device=dev, dtype=torch.float32).to(torch.float8_e4m3fn).view(torch.uint8)
+    sc8 = torch.full((b * hkv,), 0.01, device=dev, dtype=torch.float32)
+    og = torch.empty((b, hq, d), device=dev, dtype=torch.bfloat16)
+    lg = torch.empty((b, hq), device=dev, dtype=torch.float32)
+    splits = fa.decode_gqa_default_splits(b, hkv, skv)
+    wsb = fa.decode_workspace_bytes(b, hq, d, splits)
+    ws = torch.empty(wsb, device=dev, dtype=torch.uint8)
+    ms = timed(lambda: fa.decode_gqa(q8g, kc8, vc8, og, lg, b, hq, hkv, skv, d, float(1.0 / np.sqrt(d)), dtype="e4m3",
+                                     kv_strides=(skv * hkv * d, d, hkv * d), q_scale=sc8, k_scale=sc8, v_scale=sc8,
+                                     workspace=ws, workspace_bytes=wsb, stream=stream))
+    algo = 2 * b * hkv * skv * d + b * hq * d + b * hq * d * 2
+    gbs = algo / (ms * 1e-3) / 1e9
+    out[f"gqa_decode_e4m3_b{b}_hq{hq}_hkv{hkv}_skv{skv}_d{d}"] = {
+        "ms": ms, "GBps": gbs, "frac_of_measured_hbm_peak": gbs / peaks["hbm_gbs"], "splits": splits,
+        "algorithmic_bytes": algo, "tokens_per_s": b / (ms * 1e-3)}
+    del kc8, vc8, ws
     return out
 
 

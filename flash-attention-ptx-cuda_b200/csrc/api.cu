@@ -83,9 +83,10 @@ int make_tensor_map_3d(CUtensorMap* out, const void* base, int dtype, uint64_t r
 int make_tensor_map_4d(CUtensorMap* out, const void* base, int dtype, uint64_t row_elems,
                        uint64_t n_rows, uint64_t n_heads, uint64_t n_blocks, uint64_t row_stride,
                        uint64_t head_stride, uint64_t block_stride, uint32_t box_cols, uint32_t box_rows) {
-    const uint64_t es = 2;
-    const CUtensorMapDataType dt = (dtype == FA_DTYPE_BF16) ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
-                                                            : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    const uint64_t es = (dtype == FA_DTYPE_E4M3) ? 1 : 2;
+    const CUtensorMapDataType dt = (dtype == FA_DTYPE_E4M3)   ? CU_TENSOR_MAP_DATA_TYPE_UINT8
+                                   : (dtype == FA_DTYPE_BF16) ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                                              : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
     cuuint64_t dims[4]    = {row_elems, n_rows, n_heads, n_blocks};
     cuuint64_t strides[3] = {row_stride * es, head_stride * es, block_stride * es};
     cuuint32_t box[4]     = {box_cols, box_rows, 1, 1};

@@ -444,8 +444,14 @@ FA_EXPORT int fa_decode_gqa(const fa_decode_gqa_args* a) {
         return FA_ERR_INVALID_ARGUMENT;
     if (a->num_q_heads % a->num_kv_heads != 0) return FA_ERR_INVALID_ARGUMENT;
     if (!(a->scale > 0.0f) || !std::isfinite(a->scale)) return FA_ERR_INVALID_ARGUMENT;
-    if (a->dtype != FA_DTYPE_F16 && a->dtype != FA_DTYPE_BF16) return FA_ERR_UNSUPPORTED;
+    if (a->dtype != FA_DTYPE_F16 && a->dtype != FA_DTYPE_BF16 && a->dtype != FA_DTYPE_E4M3) return FA_ERR_UNSUPPORTED;
     if (a->d_head != 64 && a->d_head != 128) return FA_ERR_UNSUPPORTED;
+    const bool e4m3 = a->dtype == FA_DTYPE_E4M3;
+    if (e4m3) {                                         // e4m3 cache and query, per-(batch, KV head) scales, bf16 out
+        if (a->d_head != 128) return FA_ERR_UNSUPPORTED;
+        if (!a->q_scale || !a->k_scale || !a->v_scale) return FA_ERR_INVALID_ARGUMENT;
+    }
+    const int align_elems = e4m3 ? 16 : 8;              // strides are multiples of 16 bytes
     if (a->num_splits < 0 || a->num_splits > FA_MAX_SPLITS) return FA_ERR_UNSUPPORTED;
     const int group = a->num_q_heads / a->num_kv_heads;
     if (group > 128) return FA_ERR_UNSUPPORTED;
@@ -464,11 +470,12 @@ FA_EXPORT int fa_decode_gqa(const fa_decode_gqa_args* a) {
         if ((long long)a->block_table_stride * ps < a->seq_len_kv) return FA_ERR_INVALID_ARGUMENT;
         if (a->kv_row_stride < a->d_head || a->kv_head_stride <= 0 || a->kv_page_stride <= 0)
             return FA_ERR_INVALID_ARGUMENT;
-        if ((a->kv_row_stride % 8) || (a->kv_head_stride % 8) || (a->kv_page_stride % 8)) return FA_ERR_MISALIGNED;
-        rs = a->kv_row_stride; hs = a->kv_head_stride; bs = 8;
+        if ((a->kv_row_stride % align_elems) || (a->kv_head_stride % align_elems) || (a->kv_page_stride % align_elems))
+            return FA_ERR_MISALIGNED;
+        rs = a->kv_row_stride; hs = a->kv_head_stride; bs = 16;
     }
     if (rs < a->d_head || hs <= 0 || bs <= 0) return FA_ERR_INVALID_ARGUMENT;
-    if ((rs % 8) || (hs % 8) || (bs % 8)) return FA_ERR_MISALIGNED;
+    if ((rs % align_elems) || (hs % align_elems) || (bs % align_elems)) return FA_ERR_MISALIGNED;
     if (!aligned16(a->q) || !aligned16(a->k) || !aligned16(a->v) || !aligned16(a->o)) return FA_ERR_MISALIGNED;
     DeviceState* st = device_state();
     if (!st) return FA_ERR_CUDA;
@@ -496,11 +503,12 @@ FA_EXPORT int fa_decode_gqa(const fa_decode_gqa_args* a) {
     g.seq_lens = a->seq_lens;
     g.block_table = a->block_table; g.table_stride = a->block_table_stride;
     g.page_size = paged ? a->page_size : 0; g.n_pages = a->num_pages; g.page_stride = a->kv_page_stride;
+    g.q_scale = a->q_scale; g.k_scale = a->k_scale; g.v_scale = a->v_scale;
     g.scale = a->scale; g.stream = stream;
     int rc = launch_decode_gqa(g, st);
     if (rc != FA_OK) return rc;
     return launch_combine(o_part, lse_part, splits, a->d_head, (long long)splits * a->d_head, 1, splits,
-                          (int)rows, a->d_head, a->o, a->lse, nullptr, a->dtype, stream);
+                          (int)rows, a->d_head, a->o, a->lse, nullptr, e4m3 ? FA_DTYPE_BF16 : a->dtype, stream);
 }
 
 FA_EXPORT int fa_combine(const float* o_parts, const float* lse_parts, int n_parts, int rows,

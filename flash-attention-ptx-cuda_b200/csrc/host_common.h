@@ -73,6 +73,7 @@ struct GqaLaunch {
     const int* block_table;                   // paged cache: [batch][table_stride] page numbers, or null
     int table_stride, page_size, n_pages;
     long long page_stride;                    // elements between pages
+    const float* q_scale; const float* k_scale; const float* v_scale;   // e4m3: per (batch, KV head)
     float scale;
     cudaStream_t stream;
 };

@@ -199,7 +199,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                const float* __restrict__ k_scale, const float* __restrict__ v_scale, int* status,
                const GqaDev gq) {
     static_assert(!FP8 || (D == 128 && BF16), "e4m3 variant: d_head 128, bf16 output");
-    static_assert(!GQA || (!CAUSAL && !FP8), "grouped-query decode: one query row per head, 16-bit inputs");
+    static_assert(!GQA || !CAUSAL, "grouped-query decode: one query row per head, every key visible");
     using L = PrefillSmem<D, FP8>;
     constexpr int NBOX = L::kNBox, NK = L::NK, NV = L::NV;
     constexpr uint32_t O_COL = kNU * 128;
@@ -273,10 +273,12 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     // KV head, page); a tile is one box inside a page, or 128 / page_size boxes of one page each;
     // pages past the end of the sequence are fetched at coordinate -1, which reads as zero.
     auto load_cache_tile = [&](uint32_t dst, const CUtensorMap* tm, uint32_t bar, const Item& it, int j) {
+        constexpr int NB = FP8 ? 1 : NBOX;            // boxes per tile row: e4m3 rows are one 128-byte box
+        constexpr int XS = FP8 ? 128 : 64;            // elements per box row
         const int hkv = it.bh % gq.n_hkv, b = it.bh / gq.n_hkv;
         const int r0 = (it.t0 + j) * kBN;
         if (gq.block_table == nullptr) {
-            for (int bx = 0; bx < NBOX; bx++) tma_load_4d(dst + bx * L::kBox, tm, bar, bx * 64, r0, hkv, b);
+            for (int bx = 0; bx < NB; bx++) tma_load_4d(dst + bx * L::kBox, tm, bar, bx * XS, r0, hkv, b);
         } else {
             const int ps = 1 << gq.page_shift;
             const int rows = min(ps, kBN);            // rows per box
@@ -284,8 +286,8 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             for (int i = 0; i < kBN / rows; i++) {
                 const int rr = r0 + i * rows;
                 const int page = rr < it.kv_len ? __ldg(tbl + (rr >> gq.page_shift)) : -1;
-                for (int bx = 0; bx < NBOX; bx++)
-                    tma_load_4d(dst + bx * L::kBox + i * rows * 128, tm, bar, bx * 64, rr & (ps - 1), hkv, page);
+                for (int bx = 0; bx < NB; bx++)
+                    tma_load_4d(dst + bx * L::kBox + i * rows * 128, tm, bar, bx * XS, rr & (ps - 1), hkv, page);
             }
         }
     };
@@ -338,7 +340,10 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                         const int s8 = g & 1;
                         if (g >= 2 && !mbar_wait(smem_u32(&bar_v8e[s8]), ((g >> 1) - 1) & 1, ctl, kBarV8Empty)) { ok = false; break; }
                         mbar_arrive_expect_tx(smem_u32(&bar_v8f[s8]), L::kV8Bytes);
-                        tma_load_3d(v8_s + s8 * L::kV8Bytes, &tm_v, smem_u32(&bar_v8f[s8]), 0, j * kBN, it.bh);
+                        if constexpr (GQA)
+                            load_cache_tile(v8_s + s8 * L::kV8Bytes, &tm_v, smem_u32(&bar_v8f[s8]), it, j);
+                        else
+                            tma_load_3d(v8_s + s8 * L::kV8Bytes, &tm_v, smem_u32(&bar_v8f[s8]), 0, j * kBN, it.bh);
                     } else {
                         const int sv = g % NV;
                         // the slot was last read by P V of tile g - NV
@@ -501,6 +506,9 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                     if (!__all_sync(0xffffffffu, w)) { ok = false; break; }
                     const uint32_t src_base = v8_s + s8 * L::kV8Bytes;
                     const uint32_t dst_base = v_s + sv * L::kVBytes;
+                    // decode over a cache: rows past the sequence's end may hold stale bytes (NaN codes
+                    // included); they are written as zero so that P = 0 there cannot poison O
+                    const int valid = GQA ? it.kv_len - (it.t0 + j) * kBN : kBN;
 #pragma unroll 4
                     for (int i = 0; i < (kBN * 16) / 128; i++) {
                         const int c16 = ct + i * 128;         // 8-element group: row c16/16, group-in-row c16%16
@@ -508,6 +516,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                         const uint32_t src = src_base + rr * 128 + (((c8 >> 1) ^ (rr & 7)) << 4) + ((c8 & 1) << 3);
                         uint32_t lo, hi;
                         asm volatile("ld.shared.v2.b32 {%0, %1}, [%2];" : "=r"(lo), "=r"(hi) : "r"(src));
+                        if (GQA && rr >= valid) { lo = 0u; hi = 0u; }
                         const uint32_t w0 = e4m3x2_to_f16x2(static_cast<uint16_t>(lo & 0xFFFFu));
                         const uint32_t w1 = e4m3x2_to_f16x2(static_cast<uint16_t>(lo >> 16));
                         const uint32_t w2 = e4m3x2_to_f16x2(static_cast<uint16_t>(hi & 0xFFFFu));
@@ -794,11 +803,11 @@ int launch_instance(const fa_prefill_args& a, DeviceState* st, const CUtensorMap
     return FA_OK;
 }
 
-template <int D, bool BF16>
+template <int D, bool BF16, bool FP8>
 int launch_gqa_instance(const GqaLaunch& g, DeviceState* st, const CUtensorMap& tq, const CUtensorMap& tk,
                         const CUtensorMap& tv) {
-    using L = PrefillSmem<D, false>;
-    auto kernel = prefill_kernel<D, false, BF16, false, true>;
+    using L = PrefillSmem<D, FP8>;
+    auto kernel = prefill_kernel<D, false, BF16, FP8, true>;
     static bool configured[64] = {};
     if (!configured[st->device]) {
         FA_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
@@ -813,7 +822,7 @@ int launch_gqa_instance(const GqaLaunch& g, DeviceState* st, const CUtensorMap& 
     const GqaDev gq{g.o_part, g.lse_part, g.n_splits, g.tiles_per_split, g.group, g.n_kv_heads,
                     g.seq_lens, g.block_table, g.table_stride, page_shift};
     kernel<<<grid, kThreads, L::kTotal, g.stream>>>(tq, tk, tv, tq, nullptr, g.kv_len, n_bh, 1, (int)n_items,
-                                                    g.scale * kLog2e, nullptr, nullptr, nullptr, st->status, gq);
+                                                    g.scale * kLog2e, g.q_scale, g.k_scale, g.v_scale, st->status, gq);
     FA_CUDA_TRY(cudaGetLastError());
     return FA_OK;
 }
@@ -845,7 +854,9 @@ int launch_decode_gqa(const GqaLaunch& g, DeviceState* st) {
     CUtensorMap tq, tk, tv;
     int rc;
     // Q [B, Hq, D] seen as (batch x KV head) tiles of `group` rows; rows past the group read as zero
-    if ((rc = make_tensor_map_3d(&tq, g.q, g.dtype, g.d_head, g.group, n_bh, 64, kBM)) != FA_OK) return rc;
+    const bool e4m3 = g.dtype == FA_DTYPE_E4M3;
+    const uint32_t box_cols = e4m3 ? 128 : 64;           // 128 bytes of a row either way
+    if ((rc = make_tensor_map_3d(&tq, g.q, g.dtype, g.d_head, g.group, n_bh, box_cols, kBM)) != FA_OK) return rc;
     // dense / strided cache: (d, key, KV head, batch); paged: (d, key in page, KV head, page)
     const bool paged = g.block_table != nullptr;
     const uint64_t rows = paged ? (uint64_t)g.page_size : (uint64_t)g.kv_len;
@@ -853,12 +864,14 @@ int launch_decode_gqa(const GqaLaunch& g, DeviceState* st) {
     const uint64_t bstride = paged ? (uint64_t)g.page_stride : (uint64_t)g.batch_stride;
     const uint32_t box_rows = paged && g.page_size < kBN ? (uint32_t)g.page_size : (uint32_t)kBN;
     if ((rc = make_tensor_map_4d(&tk, g.k, g.dtype, g.d_head, rows, g.n_kv_heads, blocks, g.row_stride,
-                                 g.head_stride, bstride, 64, box_rows)) != FA_OK) return rc;
+                                 g.head_stride, bstride, box_cols, box_rows)) != FA_OK) return rc;
     if ((rc = make_tensor_map_4d(&tv, g.v, g.dtype, g.d_head, rows, g.n_kv_heads, blocks, g.row_stride,
-                                 g.head_stride, bstride, 64, box_rows)) != FA_OK) return rc;
+                                 g.head_stride, bstride, box_cols, box_rows)) != FA_OK) return rc;
+    if (e4m3) return launch_gqa_instance<128, true, true>(g, st, tq, tk, tv);
     const bool bf = g.dtype == FA_DTYPE_BF16;
-    if (g.d_head == 64) return bf ? launch_gqa_instance<64, true>(g, st, tq, tk, tv) : launch_gqa_instance<64, false>(g, st, tq, tk, tv);
-    return bf ? launch_gqa_instance<128, true>(g, st, tq, tk, tv) : launch_gqa_instance<128, false>(g, st, tq, tk, tv);
+    if (g.d_head == 64)
+        return bf ? launch_gqa_instance<64, true, false>(g, st, tq, tk, tv) : launch_gqa_instance<64, false, false>(g, st, tq, tk, tv);
+    return bf ? launch_gqa_instance<128, true, false>(g, st, tq, tk, tv) : launch_gqa_instance<128, false, false>(g, st, tq, tk, tv);
 }
 
 #ifdef FA_PHASE_TIMING

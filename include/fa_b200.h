@@ -182,6 +182,13 @@ int fa_decode_static(const fa_decode_args* args);
  *       sequence of length 0 yields O = 0 and LSE = -inf.  Cache contents past a
  *       sequence's end are never used (they may be uninitialised).
  *
+ *   dtype FA_DTYPE_E4M3 (d_head 128 only): q, k and v hold e4m3 codes, the value of an
+ *       element of sequence b, KV head h being code * {q,k,v}_scale[b * num_kv_heads + h]
+ *       (device arrays of B * num_kv_heads floats; the query heads of a group share the
+ *       scale); o is bf16; strides are multiples of 16 elements.  Q K^T runs on the 8-bit
+ *       tensor-core kind, V is converted to fp16 in shared memory (exact), P is fp16: the
+ *       cache is read at one byte per element.
+ *
  * The group of num_q_heads / num_kv_heads (<= 128) query heads that share a KV
  * head occupies the rows of one tensor-core query tile, so K and V stream from
  * HBM once per KV head whatever the group size.  The KV length is split over
@@ -202,7 +209,7 @@ typedef struct fa_decode_gqa_args {
     int         seq_len_kv;
     int         d_head;           /* 64 or 128 */
     float       scale;
-    int         dtype;            /* FA_DTYPE_F16 or FA_DTYPE_BF16 */
+    int         dtype;            /* FA_DTYPE_F16, FA_DTYPE_BF16 or FA_DTYPE_E4M3 */
     int         num_splits;       /* 0 = library chooses; else 1..FA_MAX_SPLITS */
     long long   kv_batch_stride;  /* elements; see above */
     long long   kv_head_stride;
@@ -213,6 +220,9 @@ typedef struct fa_decode_gqa_args {
     int         num_pages;
     long long   kv_page_stride;
     const int*  seq_lens;         /* device; NULL = every sequence has seq_len_kv keys */
+    const float* q_scale;         /* e4m3 only */
+    const float* k_scale;
+    const float* v_scale;
     void*       workspace;
     size_t      workspace_bytes;
     void*       stream;

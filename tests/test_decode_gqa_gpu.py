@@ -208,3 +208,59 @@ def test_gqa_sequence_lengths_on_a_dense_cache(fa, oracle, dev):
     assert fa.device_status() == 0
     assert np.abs(do.float().cpu().numpy() - o_ref).max() < 2e-3
     assert np.abs(dl.cpu().numpy() - l_ref).max() < 1e-3
+
+
+@pytest.mark.parametrize("paged", [False, True])
+def test_gqa_e4m3_cache(fa, oracle, dev, paged):
+    """e4m3 query and KV cache with per-(batch, KV head) scales, bf16 output.  The oracle runs in fp32 on
+    the dequantised values, so the comparison measures the kernel, not the quantiser; tolerance as for
+    the e4m3 prefill: O max-abs 3e-2, LSE 1e-3.  The paged variant also gives the sequences different
+    lengths and fills unused cache bytes with 0x7F (an e4m3 NaN code)."""
+    b, hq, hkv, d, smax = 2, 8, 2, 128, 1024
+    g = hq // hkv
+    lens = [1000, 333] if paged else [smax, smax]
+    scale = 1.0 / np.sqrt(d)
+    k_f, v_f = oracle.normal_inputs(900 + paged, (b * hkv, smax, d), n=2)
+    q_f = oracle.normal_inputs(902 + paged, (b * hkv, g, d), n=1)[0]          # the group shares a scale
+    (qc, qs, qd), (kc, ks, kd), (vc, vs, vd) = (oracle.quantize_e4m3(x) for x in (q_f, k_f, v_f))
+    q_deq = qd.reshape(b, hq, d)
+    k_deq, v_deq = kd.reshape(b, hkv, smax, d), vd.reshape(b, hkv, smax, d)
+    o_ref, l_ref = oracle_ragged(oracle, q_deq, k_deq, v_deq, lens, scale)
+
+    dq = torch.from_numpy(qc.reshape(b, hq, d)).to(dev)
+    sq, sk, sv = (torch.from_numpy(x).to(dev) for x in (qs, ks, vs))
+    kc4, vc4 = (torch.from_numpy(x.reshape(b, hkv, smax, d)).to(dev) for x in (kc, vc))
+    kw = {}
+    if paged:
+        ps = 64
+        pages_per_seq = smax // ps
+        n_pages = b * pages_per_seq + 3
+        perm = np.random.default_rng(5).permutation(n_pages)[: b * pages_per_seq].reshape(b, pages_per_seq)
+        kp = torch.full((n_pages, ps, hkv, d), 0x7F, device=dev, dtype=torch.uint8)
+        vp = torch.full((n_pages, ps, hkv, d), 0x7F, device=dev, dtype=torch.uint8)
+        table = np.full((b, pages_per_seq), -1, np.int32)
+        for i in range(b):
+            for pg in range((lens[i] + ps - 1) // ps):
+                r0, r1 = pg * ps, min((pg + 1) * ps, lens[i])
+                table[i, pg] = perm[i, pg]
+                kp[perm[i, pg], : r1 - r0] = kc4[i, :, r0:r1].permute(1, 0, 2)
+                vp[perm[i, pg], : r1 - r0] = vc4[i, :, r0:r1].permute(1, 0, 2)
+        kbuf, vbuf = kp, vp
+        kw = dict(kv_strides=(0, d, hkv * d), block_table=torch.from_numpy(table).to(dev),
+                  block_table_stride=pages_per_seq, page_size=ps, num_pages=n_pages, kv_page_stride=ps * hkv * d,
+                  seq_lens=torch.tensor(lens, device=dev, dtype=torch.int32))
+    else:
+        kbuf, vbuf = kc4, vc4
+    do = torch.full((b, hq, d), float("nan"), device=dev, dtype=torch.bfloat16)
+    dl = torch.full((b, hq), float("nan"), device=dev, dtype=torch.float32)
+    splits = fa.decode_gqa_default_splits(b, hkv, smax)
+    wsb = fa.decode_workspace_bytes(b, hq, d, splits)
+    ws = torch.empty(wsb, device=dev, dtype=torch.uint8)
+    fa.decode_gqa(dq, kbuf, vbuf, do, dl, b, hq, hkv, smax, d, float(scale), dtype="e4m3", q_scale=sq, k_scale=sk,
+                  v_scale=sv, workspace=ws, workspace_bytes=wsb, **kw)
+    torch.cuda.synchronize()
+    assert fa.device_status() == 0
+    o, l = do.float().cpu().numpy(), dl.cpu().numpy()
+    assert np.isfinite(o).all()
+    assert np.abs(o - o_ref).max() < 3e-2
+    assert np.abs(l - l_ref).max() < 1e-3
