@@ -647,6 +647,17 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                 if ((tid & 127) == 0 && r == 0) FA_TS(grp * 2, j, 0);
                 const int u = g % kNU;                    // the tile's score buffer; P goes back into its first half
                 const uint32_t t_s = tmem + lane_off + u * 128;
+                if constexpr (GQA) {
+                    // Decode: only the first `group` rows of the tile carry a query head.  A warp whose 32
+                    // rows are all padding has nothing to compute: it keeps step with the tile (the wait
+                    // above) and reports its part of P as done; whatever P V makes of those rows stays in
+                    // rows that are never stored.
+                    if ((warp & 3) * 32 >= gq.group) {
+                        tc_fence_before();
+                        if (lane == 0) mbar_arrive(smem_u32(&bar_pf[u]));
+                        continue;
+                    }
+                }
                 uint32_t s[128];
                 tmem_ld128_wait(t_s, s);
                 if ((tid & 127) == 0 && r == 0) FA_TS(grp * 2, j, 1);
