@@ -132,7 +132,7 @@ struct PrefillSmem {
     static constexpr int kV8Bytes = FP8 ? kBox : 0;       // landing buffers of the e4m3 V tiles
     static constexpr int kOBytes  = kNBox * kBox;         // epilogue staging (16-bit output tile)
     static constexpr int NK  = (D == 64) ? 4 : 2;
-    static constexpr int NV  = (D == 64) ? 4 : 2;
+    static constexpr int NV  = (D == 64) ? 4 : (FP8 ? 3 : 2);   // e4m3: the converted (fp16) V tiles
     static constexpr int NV8 = FP8 ? 2 : 0;
     static constexpr int kTotal = kQBytes + NK * kKBytes + NV * kVBytes + NV8 * kV8Bytes + kOBytes + 1024;
 };
