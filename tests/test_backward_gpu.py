@@ -67,3 +67,16 @@ def test_backward_argument_errors(fa, dev):
     assert fa.backward_raw(t, t, t, t, t, l, t, t, t, 1, 1, 128, 64, 0.125, False, dtype="f16", workspace=ws,
                            workspace_bytes=16) == fa.FA_ERR_WORKSPACE
     assert fa.backward_raw(t, t, t, t, t, l, t, t, t, 1, 1, 128, 64, -1.0, False, **ok) == fa.FA_ERR_INVALID_ARGUMENT
+
+
+@pytest.mark.parametrize("s", [1, 63, 65, 129])
+def test_backward_edge_lengths(fa, dev, s):
+    """Sequences shorter than one step, one row past a step and one row past a tile."""
+    g = torch.Generator().manual_seed(77 + s)
+    q, k, v, d_o = (torch.randn((2, s, 64), generator=g).half() for _ in range(4))
+    for causal in (False, True):
+        ref = autograd_reference(q, k, v, d_o, 0.125, causal)
+        got = run_backward(fa, dev, q, k, v, d_o, 0.125, causal, "f16")
+        for name, r, x in zip(("dQ", "dK", "dV"), ref, got):
+            assert torch.isfinite(x).all(), name
+            assert (x - r).abs().max().item() < 4e-3 * r.abs().max().item() + 2e-3, (name, causal)

@@ -264,3 +264,18 @@ def test_gqa_e4m3_cache(fa, oracle, dev, paged):
     assert np.isfinite(o).all()
     assert np.abs(o - o_ref).max() < 3e-2
     assert np.abs(l - l_ref).max() < 1e-3
+
+
+@pytest.mark.parametrize("b,hq,hkv,s,d,dtype", [
+    (1, 128, 1, 300, 64, "f16"),     # the largest group: every row of the query tile is a head
+    (2, 6, 2, 1, 128, "f16"),        # a single key; group of 3
+    (1, 33, 1, 257, 128, "bf16"),    # group just past one warp of rows
+])
+def test_gqa_edge_groups_and_lengths(fa, oracle, dev, b, hq, hkv, s, d, dtype):
+    scale = 1.0 / np.sqrt(d)
+    q, k, v = make(oracle, 1200 + hq + s, b, hq, hkv, s, d, dtype)
+    o, l = run_gqa(fa, dev, q, k, v, scale, dtype=dtype)
+    o_ref, l_ref = oracle_gqa(oracle, q, k, v, scale)
+    tol = 2e-3 if dtype == "f16" else 2 * 2.0 ** -8 * np.abs(o_ref).max() + 5e-3
+    assert np.abs(o - o_ref).max() < tol
+    assert np.abs(l - l_ref).max() < 1e-3
