@@ -82,6 +82,7 @@ class DecodeGqaArgs(ctypes.Structure):
         ("block_table", ctypes.c_void_p), ("block_table_stride", ctypes.c_int), ("page_size", ctypes.c_int),
         ("num_pages", ctypes.c_int), ("kv_page_stride", ctypes.c_longlong), ("seq_lens", ctypes.c_void_p),
         ("q_scale", ctypes.c_void_p), ("k_scale", ctypes.c_void_p), ("v_scale", ctypes.c_void_p),
+        ("num_q_tokens", ctypes.c_int),
         ("workspace", ctypes.c_void_p), ("workspace_bytes", ctypes.c_size_t),
         ("stream", ctypes.c_void_p),
     ]
@@ -239,7 +240,8 @@ def decode_gqa_default_splits(batch_size, num_kv_heads, seq_len_kv) -> int:
 def decode_gqa_raw(q, k, v, o, lse, batch_size, num_q_heads, num_kv_heads, seq_len_kv, d_head, scale,
                    dtype="f16", num_splits=0, kv_strides=(0, 0, 0), workspace=None, workspace_bytes=0,
                    stream=None, block_table=None, block_table_stride=0, page_size=0, num_pages=0,
-                   kv_page_stride=0, seq_lens=None, q_scale=None, k_scale=None, v_scale=None) -> int:
+                   kv_page_stride=0, seq_lens=None, q_scale=None, k_scale=None, v_scale=None,
+                   num_q_tokens=0) -> int:
     """fa_decode_gqa; ``kv_strides`` = (batch, head, row) strides of the cache in elements
     ((0, 0, 0) = dense [B, Hkv, Skv, D]); ``block_table`` (int32, device) selects the paged
     layout; ``seq_lens`` (int32, device) gives per-sequence lengths.  Returns the status code."""
@@ -247,7 +249,7 @@ def decode_gqa_raw(q, k, v, o, lse, batch_size, num_q_heads, num_kv_heads, seq_l
                       seq_len_kv, d_head, scale, DTYPES[dtype] if isinstance(dtype, str) else dtype,
                       num_splits, kv_strides[0], kv_strides[1], kv_strides[2], _ptr(block_table),
                       block_table_stride, page_size, num_pages, kv_page_stride, _ptr(seq_lens),
-                      _ptr(q_scale), _ptr(k_scale), _ptr(v_scale),
+                      _ptr(q_scale), _ptr(k_scale), _ptr(v_scale), num_q_tokens,
                       _ptr(workspace), workspace_bytes, _stream_handle(stream))
     return lib().fa_decode_gqa(ctypes.byref(a))
 

@@ -98,6 +98,24 @@ int make_tensor_map_4d(CUtensorMap* out, const void* base, int dtype, uint64_t r
     return FA_OK;
 }
 
+int make_tensor_map_q5(CUtensorMap* out, const void* base, int dtype, uint64_t d_head, uint64_t group,
+                       uint64_t n_tok, uint64_t n_kv_heads, uint64_t batch, uint32_t box_cols) {
+    const uint64_t es = (dtype == FA_DTYPE_E4M3) ? 1 : 2;
+    const CUtensorMapDataType dt = (dtype == FA_DTYPE_E4M3)   ? CU_TENSOR_MAP_DATA_TYPE_UINT8
+                                   : (dtype == FA_DTYPE_BF16) ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                                              : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    const uint64_t hq = group * n_kv_heads;
+    cuuint64_t dims[5]    = {d_head, group, n_tok, n_kv_heads, batch};
+    cuuint64_t strides[4] = {d_head * es, hq * d_head * es, group * d_head * es, n_tok * hq * d_head * es};
+    cuuint32_t box[5]     = {box_cols, (cuuint32_t)group, (cuuint32_t)n_tok, 1, 1};
+    cuuint32_t estr[5]    = {1, 1, 1, 1, 1};
+    CUresult r = g_encode(out, dt, 5, const_cast<void*>(base), dims, strides, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                          CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return note_driver_error(r, "cuTensorMapEncodeTiled");
+    return FA_OK;
+}
+
 namespace {
 
 int validate_prefill(const fa_prefill_args* a) {

@@ -454,8 +454,10 @@ FA_EXPORT int fa_decode_gqa(const fa_decode_gqa_args* a) {
     const int align_elems = e4m3 ? 16 : 8;              // strides are multiples of 16 bytes
     if (a->num_splits < 0 || a->num_splits > FA_MAX_SPLITS) return FA_ERR_UNSUPPORTED;
     const int group = a->num_q_heads / a->num_kv_heads;
-    if (group > 128) return FA_ERR_UNSUPPORTED;
-    const long long rows = (long long)a->batch_size * a->num_q_heads;
+    const int n_tok = a->num_q_tokens > 0 ? a->num_q_tokens : 1;
+    if (a->num_q_tokens < 0 || n_tok > a->seq_len_kv) return FA_ERR_INVALID_ARGUMENT;
+    if ((long long)group * n_tok > 128) return FA_ERR_UNSUPPORTED;     // one query tile per (batch, KV head)
+    const long long rows = (long long)a->batch_size * n_tok * a->num_q_heads;
     if (rows > 0x7FFFFFFFll) return FA_ERR_INVALID_ARGUMENT;
     long long rs = a->kv_row_stride, hs = a->kv_head_stride, bs = a->kv_batch_stride;
     if (rs == 0 && hs == 0 && bs == 0) {               // dense [B, Hkv, Skv, D]
@@ -487,13 +489,14 @@ FA_EXPORT int fa_decode_gqa(const fa_decode_gqa_args* a) {
     if (splits > n_tiles) splits = n_tiles;
     const int tps = (n_tiles + splits - 1) / splits;
     splits = (n_tiles + tps - 1) / tps;
-    const size_t need = fa_decode_workspace_bytes(a->batch_size, a->num_q_heads, a->d_head, splits);
+    const size_t need = fa_decode_workspace_bytes(a->batch_size, n_tok * a->num_q_heads, a->d_head, splits);
     if (!a->workspace || a->workspace_bytes < need || !aligned16(a->workspace)) return FA_ERR_WORKSPACE;
     float* o_part = static_cast<float*>(a->workspace);
     float* lse_part = reinterpret_cast<float*>(static_cast<uint8_t*>(a->workspace) +
                                                align256((size_t)rows * splits * a->d_head * sizeof(float)));
     cudaStream_t stream = static_cast<cudaStream_t>(a->stream);
     GqaLaunch g{};
+    g.n_tok = n_tok;
     g.q = a->q; g.k = a->k; g.v = a->v;
     g.o_part = o_part; g.lse_part = lse_part;
     g.batch = a->batch_size; g.n_kv_heads = a->num_kv_heads; g.group = group;

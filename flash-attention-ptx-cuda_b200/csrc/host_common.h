@@ -55,6 +55,11 @@ int make_tensor_map_4d(CUtensorMap* out, const void* base, int dtype, uint64_t r
                        uint64_t n_rows, uint64_t n_heads, uint64_t n_blocks, uint64_t row_stride,
                        uint64_t head_stride, uint64_t block_stride, uint32_t box_cols, uint32_t box_rows);
 
+// Rank-5 tensor map over the decode queries [B, T, Hq, D] seen as (d, head in group, token, KV head,
+// batch): one box holds the `group` x `n_tok` rows of a (batch, KV head) pair, token-major.
+int make_tensor_map_q5(CUtensorMap* out, const void* base, int dtype, uint64_t d_head, uint64_t group,
+                       uint64_t n_tok, uint64_t n_kv_heads, uint64_t batch, uint32_t box_cols);
+
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 // Implemented next to their kernels.
@@ -67,6 +72,7 @@ struct GqaLaunch {
     const void* q; const void* k; const void* v;
     float* o_part; float* lse_part;           // [row][split][D] and [row][split], row = b * Hq + hq
     int batch, n_kv_heads, group, kv_len, d_head, dtype;
+    int n_tok;                                // query tokens per sequence (1 = plain decode)
     int n_splits, tiles_per_split;
     long long row_stride, head_stride, batch_stride;   // of the KV cache, in elements
     const int* seq_lens;                      // [batch] or null

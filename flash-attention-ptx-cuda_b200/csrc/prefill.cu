@@ -142,6 +142,8 @@ struct GqaDev {
     float* o_part;          // [row][split][D] fp32, row = (batch x KV head) * group + query head in group
     float* lse_part;        // [row][split]
     int n_splits, tiles_per_split, group, n_hkv;
+    int n_tok;              // query tokens per sequence; row r of the query tile is token r / group, head r % group
+    int live_rows;          // n_tok * group
     const int* seq_lens;    // per-sequence KV lengths, or null: every sequence has seq_len keys
     const int* block_table; // paged cache: [batch][table_stride] page numbers, or null
     int table_stride;
@@ -151,6 +153,15 @@ struct GqaDev {
 // Work list: item index -> (query tile, head), heaviest first when causal.  In grouped-query
 // decode mode an item is (batch x KV head, KV split): key tiles [t0, t0 + n_kv) of that head.
 struct Item { int q_start, bh, n_kv, t0, split, kv_len; bool empty; };
+
+// Index of the partial result of tile row r: output row ((batch * n_tok + token) * Hq + query head),
+// then the KV split.
+__device__ __forceinline__ size_t gqa_partial_index(const GqaDev& gq, const Item& it, int r) {
+    const int b = it.bh / gq.n_hkv, hkv = it.bh - b * gq.n_hkv;
+    const int t = r / gq.group, g = r - t * gq.group;
+    const size_t row = (static_cast<size_t>(b) * gq.n_tok + t) * (gq.n_hkv * gq.group) + hkv * gq.group + g;
+    return row * gq.n_splits + it.split;
+}
 
 template <bool CAUSAL, bool GQA>
 __device__ __forceinline__ bool get_item(int k, int n_items, int n_bh, int n_qtiles, int seq_len,
@@ -256,6 +267,13 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         fence_mbar_init();
     }
     if (tid < 256) m_slot[tid >> 7][tid & 127] = make_uint2(0u, 0xFFFFFFFFu);   // no tile has this index
+    if constexpr (GQA) {
+        // decode: a Q load only writes the rows that carry a (token, head) pair; the other rows of the
+        // query tile are zero for the whole launch
+        for (int i = tid; i < L::kQBytes / 16; i += kThreads)
+            asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(q_s + i * 16), "r"(0u) : "memory");
+        fence_proxy_async_smem();
+    }
     if (warp == 8 && lane == 0) {
         prefetch_tensormap(&tm_q); prefetch_tensormap(&tm_k);
         prefetch_tensormap(&tm_v); prefetch_tensormap(&tm_o);
@@ -306,9 +324,17 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                 Item it;
                 if (!get_item<CAUSAL, GQA>(r, n_items, n_bh, n_qtiles, seq_len, gq, it)) continue;
                 if (it_n > 0 && !mbar_wait(smem_u32(&bar_qe), (it_n - 1) & 1, ctl, kBarQEmpty)) break;
-                mbar_arrive_expect_tx(smem_u32(&bar_qf), L::kQBytes);
-                for (int b = 0; b < NLOAD; b++)
-                    tma_load_3d(q_s + b * L::kBox, &tm_q, smem_u32(&bar_qf), b * XSTEP, it.q_start, it.bh);
+                if constexpr (GQA) {
+                    // the box holds only the live rows (token-major); the rest of the tile stays zero
+                    mbar_arrive_expect_tx(smem_u32(&bar_qf), NLOAD * gq.live_rows * 128);
+                    for (int b = 0; b < NLOAD; b++)
+                        tma_load_5d(q_s + b * L::kBox, &tm_q, smem_u32(&bar_qf), b * XSTEP, 0, 0, it.bh % gq.n_hkv,
+                                    it.bh / gq.n_hkv);
+                } else {
+                    mbar_arrive_expect_tx(smem_u32(&bar_qf), L::kQBytes);
+                    for (int b = 0; b < NLOAD; b++)
+                        tma_load_3d(q_s + b * L::kBox, &tm_q, smem_u32(&bar_qf), b * XSTEP, it.q_start, it.bh);
+                }
                 for (int j = 0; j < it.n_kv; j++, g++) {
                     const int sk = g % NK;
                     // the slot was last read by Q K^T of tile g - NK
@@ -487,8 +513,8 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             if (!get_item<CAUSAL, GQA>(r, n_items, n_bh, n_qtiles, seq_len, gq, it)) {
                 if constexpr (GQA) {
                     // a KV split past the end of a short sequence: weight zero in the merge
-                    if (it.empty && r_in_tile < gq.group) {
-                        const size_t pidx = (static_cast<size_t>(it.bh) * gq.group + r_in_tile) * gq.n_splits + it.split;
+                    if (it.empty && r_in_tile < gq.live_rows) {
+                        const size_t pidx = gqa_partial_index(gq, it, r_in_tile);
                         gq.lse_part[pidx] = -INFINITY;
                         float4* dst = reinterpret_cast<float4*>(gq.o_part + pidx * D);
                         for (int e = 0; e < D / 4; e++) dst[e] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
@@ -550,9 +576,12 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             if constexpr (GQA) {
                 // Partial result of this KV split: normalised fp32 O and its LSE for the rows that
                 // carry a query head; the merge over splits is a separate kernel.
-                const bool live = r_in_tile < gq.group;
-                const size_t pidx = (static_cast<size_t>(it.bh) * gq.group + r_in_tile) * gq.n_splits + it.split;
-                if (live) gq.lse_part[pidx] = kLn2 * (m_fin + log2f(l_run));
+                const bool live = r_in_tile < gq.live_rows;
+                const size_t pidx = gqa_partial_index(gq, it, r_in_tile);
+                // a token with no visible key (a sequence shorter than the token count): O = 0, LSE = -inf
+                const bool seen = l_run > 0.0f;
+                if (!seen) inv_l = 0.0f;
+                if (live) gq.lse_part[pidx] = seen ? kLn2 * (m_fin + log2f(l_run)) : -INFINITY;
 #pragma unroll 1
                 for (int c = 0; c < D / 32; c++) {
                     uint32_t o[32];
@@ -625,8 +654,13 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             Item it;
             if (!get_item<CAUSAL, GQA>(r, n_items, n_bh, n_qtiles, seq_len, gq, it)) continue;
             const int row = it.q_start + r_in_tile;
-            const int row_limit = CAUSAL ? min(seq_len, row + 1) : it.kv_len;   // keys [0,row_limit) visible
-            const int tile_min_limit = CAUSAL ? min(seq_len, it.q_start + 1) : it.kv_len;
+            // keys [0,row_limit) visible.  Decode with several query tokens: they are the last n_tok
+            // entries of the cache, token t sees everything up to and including itself.
+            const int row_limit = CAUSAL ? min(seq_len, row + 1)
+                                  : GQA  ? max(0, min(it.kv_len, it.kv_len - gq.n_tok + 1 + r_in_tile / gq.group))
+                                         : it.kv_len;
+            const int tile_min_limit = CAUSAL ? min(seq_len, it.q_start + 1)
+                                       : GQA  ? max(0, it.kv_len - gq.n_tok + 1) : it.kv_len;
             float scale_log2 = scale_log2_in;
             if constexpr (FP8) scale_log2 *= q_scale[it.bh] * k_scale[it.bh];
             const uint64_t scale2 = pack2(scale_log2, scale_log2);
@@ -652,7 +686,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                     // rows are all padding has nothing to compute: it keeps step with the tile (the wait
                     // above) and reports its part of P as done; whatever P V makes of those rows stays in
                     // rows that are never stored.
-                    if ((warp & 3) * 32 >= gq.group) {
+                    if ((warp & 3) * 32 >= gq.live_rows) {
                         tc_fence_before();
                         if (lane == 0) mbar_arrive(smem_u32(&bar_pf[u]));
                         continue;
@@ -831,7 +865,7 @@ int launch_gqa_instance(const GqaLaunch& g, DeviceState* st, const CUtensorMap& 
     int page_shift = 0;
     while ((1 << page_shift) < g.page_size) page_shift++;
     const GqaDev gq{g.o_part, g.lse_part, g.n_splits, g.tiles_per_split, g.group, g.n_kv_heads,
-                    g.seq_lens, g.block_table, g.table_stride, page_shift};
+                    g.n_tok, g.n_tok * g.group, g.seq_lens, g.block_table, g.table_stride, page_shift};
     kernel<<<grid, kThreads, L::kTotal, g.stream>>>(tq, tk, tv, tq, nullptr, g.kv_len, n_bh, 1, (int)n_items,
                                                     g.scale * kLog2e, g.q_scale, g.k_scale, g.v_scale, st->status, gq);
     FA_CUDA_TRY(cudaGetLastError());
@@ -861,13 +895,13 @@ int launch_prefill_16bit(const fa_prefill_args& a, DeviceState* st) {
 }
 
 int launch_decode_gqa(const GqaLaunch& g, DeviceState* st) {
-    const uint64_t n_bh = (uint64_t)g.batch * g.n_kv_heads;
     CUtensorMap tq, tk, tv;
     int rc;
-    // Q [B, Hq, D] seen as (batch x KV head) tiles of `group` rows; rows past the group read as zero
+    // Q [B, T, Hq, D]: one box per (batch, KV head) with its group x T rows, token-major
     const bool e4m3 = g.dtype == FA_DTYPE_E4M3;
     const uint32_t box_cols = e4m3 ? 128 : 64;           // 128 bytes of a row either way
-    if ((rc = make_tensor_map_3d(&tq, g.q, g.dtype, g.d_head, g.group, n_bh, box_cols, kBM)) != FA_OK) return rc;
+    if ((rc = make_tensor_map_q5(&tq, g.q, g.dtype, g.d_head, g.group, g.n_tok, g.n_kv_heads, g.batch, box_cols)) != FA_OK)
+        return rc;
     // dense / strided cache: (d, key, KV head, batch); paged: (d, key in page, KV head, page)
     const bool paged = g.block_table != nullptr;
     const uint64_t rows = paged ? (uint64_t)g.page_size : (uint64_t)g.kv_len;

@@ -189,6 +189,12 @@ int fa_decode_static(const fa_decode_args* args);
  *       tensor-core kind, V is converted to fp16 in shared memory (exact), P is fp16: the
  *       cache is read at one byte per element.
  *
+ *   num_q_tokens = T > 1 (speculative / multi-token decode, appended chunks): q and o are
+ *       [B, T, Hq, D], lse [B, T, Hq]; the T tokens are the last T entries of each sequence's
+ *       cache and token t sees keys [0, len - T + t]; T * (num_q_heads / num_kv_heads) <= 128;
+ *       the workspace is fa_decode_workspace_bytes(B, T * Hq, D, splits).  A token of a sequence
+ *       shorter than T that sees no key yields O = 0, LSE = -inf.
+ *
  * The group of num_q_heads / num_kv_heads (<= 128) query heads that share a KV
  * head occupies the rows of one tensor-core query tile, so K and V stream from
  * HBM once per KV head whatever the group size.  The KV length is split over
@@ -223,6 +229,7 @@ typedef struct fa_decode_gqa_args {
     const float* q_scale;         /* e4m3 only */
     const float* k_scale;
     const float* v_scale;
+    int         num_q_tokens;     /* 0 or 1 = one query token per sequence */
     void*       workspace;
     size_t      workspace_bytes;
     void*       stream;

@@ -279,3 +279,60 @@ def test_gqa_edge_groups_and_lengths(fa, oracle, dev, b, hq, hkv, s, d, dtype):
     tol = 2e-3 if dtype == "f16" else 2 * 2.0 ** -8 * np.abs(o_ref).max() + 5e-3
     assert np.abs(o - o_ref).max() < tol
     assert np.abs(l - l_ref).max() < 1e-3
+
+
+def oracle_multi_token(oracle, q, k, v, lens, scale):
+    """q [B,T,Hq,D]; token t of sequence b sees keys [0, lens[b] - T + t]."""
+    b, t_n, hq, d = q.shape
+    o = np.zeros((b, t_n, hq, d), np.float32)
+    l = np.full((b, t_n, hq), -np.inf, np.float32)
+    for i in range(b):
+        for t in range(t_n):
+            vis = lens[i] - t_n + t + 1
+            if vis > 0:
+                oi, li = oracle_gqa(oracle, q[i:i + 1, t], k[i:i + 1, :, :vis], v[i:i + 1, :, :vis], scale)
+                o[i, t], l[i, t] = oi[0], li[0]
+    return o, l
+
+
+@pytest.mark.parametrize("b,t_n,hq,hkv,smax,d,lens", [
+    (2, 4, 8, 2, 700, 128, None),            # 4 draft tokens, group 4
+    (1, 8, 8, 1, 1024, 64, None),            # 8 tokens x 8 heads = 64 rows of the tile
+    (3, 3, 4, 4, 512, 128, [512, 130, 2]),   # ragged; the last sequence is shorter than the token count
+    (1, 16, 8, 1, 300, 128, None),           # the full tile: 16 x 8 = 128 rows
+])
+def test_multi_token_decode(fa, oracle, dev, b, t_n, hq, hkv, smax, d, lens):
+    scale = 1.0 / np.sqrt(d)
+    q = oracle.round_to(oracle.normal_inputs(1500 + t_n, (b, t_n, hq, d), n=1)[0], "f16")
+    k, v = (oracle.round_to(x, "f16") for x in oracle.normal_inputs(1501 + t_n, (b, hkv, smax, d), n=2))
+    o_ref, l_ref = oracle_multi_token(oracle, q, k, v, lens or [smax] * b, scale)
+    dq, dk, dv = (to_dev(x, "f16", dev) for x in (q, k, v))
+    kw = {}
+    if lens is not None:
+        for i in range(b):
+            dk[i, :, lens[i]:] = float("nan")
+            dv[i, :, lens[i]:] = float("nan")
+        kw["seq_lens"] = torch.tensor(lens, device=dev, dtype=torch.int32)
+    do = torch.full((b, t_n, hq, d), float("nan"), device=dev, dtype=torch.float16)
+    dl = torch.full((b, t_n, hq), float("nan"), device=dev, dtype=torch.float32)
+    splits = fa.decode_gqa_default_splits(b, hkv, smax)
+    wsb = fa.decode_workspace_bytes(b, t_n * hq, d, splits)
+    ws = torch.full((wsb // 4,), float("nan"), device=dev, dtype=torch.float32)
+    fa.decode_gqa(dq, dk, dv, do, dl, b, hq, hkv, smax, d, float(scale), dtype="f16", num_q_tokens=t_n,
+                  workspace=ws, workspace_bytes=wsb, **kw)
+    torch.cuda.synchronize()
+    assert fa.device_status() == 0
+    o, l = do.float().cpu().numpy(), dl.cpu().numpy()
+    assert np.isfinite(o).all()
+    assert np.abs(o - o_ref).max() < 2e-3
+    live = np.isfinite(l_ref)
+    assert np.abs(l[live] - l_ref[live]).max() < 1e-3
+    assert np.all(np.isneginf(l[~live]))
+
+
+def test_multi_token_decode_argument_errors(fa, dev):
+    t = torch.zeros(1 << 16, device=dev, dtype=torch.float16)
+    ws = torch.empty(1 << 22, device=dev, dtype=torch.uint8)
+    ok = dict(dtype="f16", workspace=ws, workspace_bytes=ws.numel())
+    assert fa.decode_gqa_raw(t, t, t, t, None, 1, 32, 1, 256, 64, 0.1, num_q_tokens=5, **ok) == fa.FA_ERR_UNSUPPORTED   # 5 x 32 rows
+    assert fa.decode_gqa_raw(t, t, t, t, None, 1, 4, 1, 2, 64, 0.1, num_q_tokens=3, **ok) == fa.FA_ERR_INVALID_ARGUMENT # more tokens than keys
