@@ -107,7 +107,8 @@ int make_tensor_map_q5(CUtensorMap* out, const void* base, int dtype, uint64_t d
     const uint64_t hq = group * n_kv_heads;
     cuuint64_t dims[5]    = {d_head, group, n_tok, n_kv_heads, batch};
     cuuint64_t strides[4] = {d_head * es, hq * d_head * es, group * d_head * es, n_tok * hq * d_head * es};
-    cuuint32_t box[5]     = {box_cols, (cuuint32_t)group, (cuuint32_t)n_tok, 1, 1};
+    const uint64_t per_tile = 128 / group < n_tok ? 128 / group : n_tok;     // tokens per query tile
+    cuuint32_t box[5]     = {box_cols, (cuuint32_t)group, (cuuint32_t)per_tile, 1, 1};
     cuuint32_t estr[5]    = {1, 1, 1, 1, 1};
     CUresult r = g_encode(out, dt, 5, const_cast<void*>(base), dims, strides, box, estr,
                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,

@@ -456,7 +456,8 @@ FA_EXPORT int fa_decode_gqa(const fa_decode_gqa_args* a) {
     const int group = a->num_q_heads / a->num_kv_heads;
     const int n_tok = a->num_q_tokens > 0 ? a->num_q_tokens : 1;
     if (a->num_q_tokens < 0 || n_tok > a->seq_len_kv) return FA_ERR_INVALID_ARGUMENT;
-    if ((long long)group * n_tok > 128) return FA_ERR_UNSUPPORTED;     // one query tile per (batch, KV head)
+    if (group > 128) return FA_ERR_UNSUPPORTED;                         // the group must fit one query tile
+
     const long long rows = (long long)a->batch_size * n_tok * a->num_q_heads;
     if (rows > 0x7FFFFFFFll) return FA_ERR_INVALID_ARGUMENT;
     long long rs = a->kv_row_stride, hs = a->kv_head_stride, bs = a->kv_batch_stride;
@@ -484,8 +485,10 @@ FA_EXPORT int fa_decode_gqa(const fa_decode_gqa_args* a) {
     if (st->cc_major != 10) return FA_ERR_NOT_SM100;
 
     const int n_tiles = (a->seq_len_kv + 127) / 128;
+    const int tok_per_tile = 128 / group < n_tok ? 128 / group : n_tok;
+    const int n_qt = (n_tok + tok_per_tile - 1) / tok_per_tile;     // query tiles per (batch, KV head)
     int splits = a->num_splits ? a->num_splits
-                               : gqa_splits(st->sm_count, (long long)a->batch_size * a->num_kv_heads, a->seq_len_kv);
+                               : gqa_splits(st->sm_count, (long long)a->batch_size * a->num_kv_heads * n_qt, a->seq_len_kv);
     if (splits > n_tiles) splits = n_tiles;
     const int tps = (n_tiles + splits - 1) / splits;
     splits = (n_tiles + tps - 1) / tps;

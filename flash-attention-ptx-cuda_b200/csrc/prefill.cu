@@ -142,8 +142,10 @@ struct GqaDev {
     float* o_part;          // [row][split][D] fp32, row = (batch x KV head) * group + query head in group
     float* lse_part;        // [row][split]
     int n_splits, tiles_per_split, group, n_hkv;
-    int n_tok;              // query tokens per sequence; row r of the query tile is token r / group, head r % group
-    int live_rows;          // n_tok * group
+    int n_tok;              // query tokens per sequence
+    int tok_per_tile;       // tokens per query tile (row r of a tile: token r / group, head r % group)
+    int n_qt;               // query tiles per (batch, KV head) = ceil(n_tok / tok_per_tile)
+    int live_rows;          // rows of a tile a Q load writes = min(tok_per_tile, n_tok) * group
     const int* seq_lens;    // per-sequence KV lengths, or null: every sequence has seq_len keys
     const int* block_table; // paged cache: [batch][table_stride] page numbers, or null
     int table_stride;
@@ -152,14 +154,14 @@ struct GqaDev {
 
 // Work list: item index -> (query tile, head), heaviest first when causal.  In grouped-query
 // decode mode an item is (batch x KV head, KV split): key tiles [t0, t0 + n_kv) of that head.
-struct Item { int q_start, bh, n_kv, t0, split, kv_len; bool empty; };
+struct Item { int q_start, bh, n_kv, t0, split, kv_len, tok0; bool empty; };
 
 // Index of the partial result of tile row r: output row ((batch * n_tok + token) * Hq + query head),
 // then the KV split.
 __device__ __forceinline__ size_t gqa_partial_index(const GqaDev& gq, const Item& it, int r) {
     const int b = it.bh / gq.n_hkv, hkv = it.bh - b * gq.n_hkv;
-    const int t = r / gq.group, g = r - t * gq.group;
-    const size_t row = (static_cast<size_t>(b) * gq.n_tok + t) * (gq.n_hkv * gq.group) + hkv * gq.group + g;
+    const int tl = r / gq.group, g = r - tl * gq.group;
+    const size_t row = (static_cast<size_t>(b) * gq.n_tok + it.tok0 + tl) * (gq.n_hkv * gq.group) + hkv * gq.group + g;
     return row * gq.n_splits + it.split;
 }
 
@@ -171,11 +173,15 @@ __device__ __forceinline__ bool get_item(int k, int n_items, int n_bh, int n_qti
         const int idx = k * G + c;                    // items are (nearly) equal: plain round-robin
         it.empty = false;
         if (idx >= n_items) return false;
-        it.bh = idx / gq.n_splits;
-        it.split = idx - it.bh * gq.n_splits;
+        const int bq = idx / gq.n_splits;             // (batch x KV head, query tile)
+        it.split = idx - bq * gq.n_splits;
+        it.bh = bq / gq.n_qt;
+        it.tok0 = (bq - it.bh * gq.n_qt) * gq.tok_per_tile;
         it.t0 = it.split * gq.tiles_per_split;
         it.kv_len = gq.seq_lens ? min(seq_len, max(0, __ldg(gq.seq_lens + it.bh / gq.n_hkv))) : seq_len;
-        it.n_kv = min(gq.tiles_per_split, (it.kv_len + kBN - 1) / kBN - it.t0);
+        // keys the tile's last token sees (the query tokens are the last n_tok entries of the cache)
+        const int kv_vis = min(it.kv_len, it.kv_len - gq.n_tok + min(gq.n_tok, it.tok0 + gq.tok_per_tile));
+        it.n_kv = min(gq.tiles_per_split, (max(kv_vis, 0) + kBN - 1) / kBN - it.t0);
         it.q_start = 0;
         // a split that lies wholly past the end of a short sequence: no role touches it, the
         // epilogue warps only record an empty partial
@@ -185,6 +191,7 @@ __device__ __forceinline__ bool get_item(int k, int n_items, int n_bh, int n_qti
     it.t0 = 0;
     it.split = 0;
     it.kv_len = seq_len;
+    it.tok0 = 0;
     it.empty = false;
     const int idx = (k & 1) ? k * G + (G - 1 - c) : k * G + c;     // boustrophedon deal
     if (idx >= n_items) return false;
@@ -328,7 +335,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                     // the box holds only the live rows (token-major); the rest of the tile stays zero
                     mbar_arrive_expect_tx(smem_u32(&bar_qf), NLOAD * gq.live_rows * 128);
                     for (int b = 0; b < NLOAD; b++)
-                        tma_load_5d(q_s + b * L::kBox, &tm_q, smem_u32(&bar_qf), b * XSTEP, 0, 0, it.bh % gq.n_hkv,
+                        tma_load_5d(q_s + b * L::kBox, &tm_q, smem_u32(&bar_qf), b * XSTEP, 0, it.tok0, it.bh % gq.n_hkv,
                                     it.bh / gq.n_hkv);
                 } else {
                     mbar_arrive_expect_tx(smem_u32(&bar_qf), L::kQBytes);
@@ -513,7 +520,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             if (!get_item<CAUSAL, GQA>(r, n_items, n_bh, n_qtiles, seq_len, gq, it)) {
                 if constexpr (GQA) {
                     // a KV split past the end of a short sequence: weight zero in the merge
-                    if (it.empty && r_in_tile < gq.live_rows) {
+                    if (it.empty && r_in_tile < gq.live_rows && it.tok0 + r_in_tile / gq.group < gq.n_tok) {
                         const size_t pidx = gqa_partial_index(gq, it, r_in_tile);
                         gq.lse_part[pidx] = -INFINITY;
                         float4* dst = reinterpret_cast<float4*>(gq.o_part + pidx * D);
@@ -576,7 +583,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             if constexpr (GQA) {
                 // Partial result of this KV split: normalised fp32 O and its LSE for the rows that
                 // carry a query head; the merge over splits is a separate kernel.
-                const bool live = r_in_tile < gq.live_rows;
+                const bool live = r_in_tile < gq.live_rows && it.tok0 + r_in_tile / gq.group < gq.n_tok;
                 const size_t pidx = gqa_partial_index(gq, it, r_in_tile);
                 // a token with no visible key (a sequence shorter than the token count): O = 0, LSE = -inf
                 const bool seen = l_run > 0.0f;
@@ -657,10 +664,10 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             // keys [0,row_limit) visible.  Decode with several query tokens: they are the last n_tok
             // entries of the cache, token t sees everything up to and including itself.
             const int row_limit = CAUSAL ? min(seq_len, row + 1)
-                                  : GQA  ? max(0, min(it.kv_len, it.kv_len - gq.n_tok + 1 + r_in_tile / gq.group))
+                                  : GQA  ? max(0, min(it.kv_len, it.kv_len - gq.n_tok + 1 + it.tok0 + r_in_tile / gq.group))
                                          : it.kv_len;
             const int tile_min_limit = CAUSAL ? min(seq_len, it.q_start + 1)
-                                       : GQA  ? max(0, it.kv_len - gq.n_tok + 1) : it.kv_len;
+                                       : GQA  ? max(0, min(it.kv_len, it.kv_len - gq.n_tok + 1 + it.tok0)) : it.kv_len;
             float scale_log2 = scale_log2_in;
             if constexpr (FP8) scale_log2 *= q_scale[it.bh] * k_scale[it.bh];
             const uint64_t scale2 = pack2(scale_log2, scale_log2);
@@ -859,13 +866,16 @@ int launch_gqa_instance(const GqaLaunch& g, DeviceState* st, const CUtensorMap& 
         configured[st->device] = true;
     }
     const int n_bh = g.batch * g.n_kv_heads;
-    const long long n_items = (long long)n_bh * g.n_splits;
+    const int tok_per_tile = kBM / g.group < g.n_tok ? kBM / g.group : g.n_tok;
+    const int n_qt = (g.n_tok + tok_per_tile - 1) / tok_per_tile;
+    const long long n_items = (long long)n_bh * n_qt * g.n_splits;
     if (n_items > 0x7FFFFFFFll) return FA_ERR_INVALID_ARGUMENT;
     const unsigned grid = (unsigned)(n_items < st->sm_count ? n_items : st->sm_count);
     int page_shift = 0;
     while ((1 << page_shift) < g.page_size) page_shift++;
     const GqaDev gq{g.o_part, g.lse_part, g.n_splits, g.tiles_per_split, g.group, g.n_kv_heads,
-                    g.n_tok, g.n_tok * g.group, g.seq_lens, g.block_table, g.table_stride, page_shift};
+                    g.n_tok, tok_per_tile, n_qt, tok_per_tile * g.group, g.seq_lens, g.block_table, g.table_stride,
+                    page_shift};
     kernel<<<grid, kThreads, L::kTotal, g.stream>>>(tq, tk, tv, tq, nullptr, g.kv_len, n_bh, 1, (int)n_items,
                                                     g.scale * kLog2e, g.q_scale, g.k_scale, g.v_scale, st->status, gq);
     FA_CUDA_TRY(cudaGetLastError());

@@ -191,9 +191,11 @@ int fa_decode_static(const fa_decode_args* args);
  *
  *   num_q_tokens = T > 1 (speculative / multi-token decode, appended chunks): q and o are
  *       [B, T, Hq, D], lse [B, T, Hq]; the T tokens are the last T entries of each sequence's
- *       cache and token t sees keys [0, len - T + t]; T * (num_q_heads / num_kv_heads) <= 128;
- *       the workspace is fa_decode_workspace_bytes(B, T * Hq, D, splits).  A token of a sequence
- *       shorter than T that sees no key yields O = 0, LSE = -inf.
+ *       cache and token t sees keys [0, len - T + t] (any T: 128 / group tokens share a query
+ *       tile, so a long T is a prefill chunk appended to a cached prefix); the workspace is
+ *       fa_decode_workspace_bytes(B, T * Hq, D, splits), and with num_splits = 0 the library
+ *       uses fa_decode_gqa_default_splits(B * ceil(T / (128 / group)), Hkv, Skv).  A token of a
+ *       sequence shorter than T that sees no key yields O = 0, LSE = -inf.
  *
  * The group of num_q_heads / num_kv_heads (<= 128) query heads that share a KV
  * head occupies the rows of one tensor-core query tile, so K and V stream from

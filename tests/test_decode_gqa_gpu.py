@@ -300,6 +300,9 @@ def oracle_multi_token(oracle, q, k, v, lens, scale):
     (1, 8, 8, 1, 1024, 64, None),            # 8 tokens x 8 heads = 64 rows of the tile
     (3, 3, 4, 4, 512, 128, [512, 130, 2]),   # ragged; the last sequence is shorter than the token count
     (1, 16, 8, 1, 300, 128, None),           # the full tile: 16 x 8 = 128 rows
+    (2, 40, 8, 1, 700, 128, None),           # 40 tokens x 8 heads: three query tiles per KV head
+    (1, 300, 2, 2, 1000, 64, None),          # a 300-token chunk appended to a 700-key prefix, group 1
+    (2, 50, 6, 2, 600, 128, [600, 45]),      # group 3 (42 tokens per tile); second sequence shorter than the chunk
 ])
 def test_multi_token_decode(fa, oracle, dev, b, t_n, hq, hkv, smax, d, lens):
     scale = 1.0 / np.sqrt(d)
@@ -334,5 +337,4 @@ def test_multi_token_decode_argument_errors(fa, dev):
     t = torch.zeros(1 << 16, device=dev, dtype=torch.float16)
     ws = torch.empty(1 << 22, device=dev, dtype=torch.uint8)
     ok = dict(dtype="f16", workspace=ws, workspace_bytes=ws.numel())
-    assert fa.decode_gqa_raw(t, t, t, t, None, 1, 32, 1, 256, 64, 0.1, num_q_tokens=5, **ok) == fa.FA_ERR_UNSUPPORTED   # 5 x 32 rows
     assert fa.decode_gqa_raw(t, t, t, t, None, 1, 4, 1, 2, 64, 0.1, num_q_tokens=3, **ok) == fa.FA_ERR_INVALID_ARGUMENT # more tokens than keys
