@@ -338,3 +338,31 @@ def test_multi_token_decode_argument_errors(fa, dev):
     ws = torch.empty(1 << 22, device=dev, dtype=torch.uint8)
     ok = dict(dtype="f16", workspace=ws, workspace_bytes=ws.numel())
     assert fa.decode_gqa_raw(t, t, t, t, None, 1, 4, 1, 2, 64, 0.1, num_q_tokens=3, **ok) == fa.FA_ERR_INVALID_ARGUMENT # more tokens than keys
+
+
+def test_whole_sequence_as_chunk_equals_causal_prefill(fa, oracle, dev):
+    """With T = Skv and one query head per KV head the chunk path computes causal self-attention:
+    it must agree with fa_prefill on the same data (both within tolerance of each other)."""
+    b, h, s, d = 2, 3, 700, 64
+    scale = 1.0 / np.sqrt(d)
+    q, k, v = (oracle.round_to(x, "f16") for x in oracle.normal_inputs(1700, (b * h, s, d)))
+    dq, dk, dv = (to_dev(x, "f16", dev) for x in (q, k, v))
+    o1 = torch.empty_like(dq)
+    l1 = torch.empty((b * h, s), device=dev, dtype=torch.float32)
+    fa.prefill(dq, dk, dv, o1, l1, b, h, s, d, float(scale), True, dtype="f16")
+    # chunk path: q, o as [B, T, Hq, D]; cache [B, Hkv, Skv, D]
+    q4 = dq.view(b, h, s, d).permute(0, 2, 1, 3).contiguous()
+    o2 = torch.full((b, s, h, d), float("nan"), device=dev, dtype=torch.float16)
+    l2 = torch.full((b, s, h), float("nan"), device=dev, dtype=torch.float32)
+    n_qt = (s + 127) // 128
+    splits = fa.decode_gqa_default_splits(b * n_qt, h, s)
+    wsb = fa.decode_workspace_bytes(b, s * h, d, splits)
+    ws = torch.empty(wsb, device=dev, dtype=torch.uint8)
+    fa.decode_gqa(q4, dk.view(b, h, s, d), dv.view(b, h, s, d), o2, l2, b, h, h, s, d, float(scale), dtype="f16",
+                  num_q_tokens=s, workspace=ws, workspace_bytes=wsb)
+    torch.cuda.synchronize()
+    assert fa.device_status() == 0
+    o2p = o2.permute(0, 2, 1, 3).reshape(b * h, s, d)
+    l2p = l2.permute(0, 2, 1).reshape(b * h, s)
+    assert (o2p.float() - o1.float()).abs().max().item() < 2e-3
+    assert (l2p - l1).abs().max().item() < 1e-3
