@@ -1,5 +1,5 @@
 """PyTorch custom operators over the C ABI: ``torch.ops.fa_b200.prefill`` / ``decode`` /
-``prefill_backward``.
+``decode_gqa`` / ``prefill_backward``.
 
 ``prefill`` is differentiable with respect to q, k and v (``fa_backward``); the gradient of its LSE
 output is not supported.  ``decode`` is forward only.  Tensors use the layout of
@@ -127,6 +127,59 @@ def _(q, k, v, scale, num_splits):
     return torch.empty_like(q), q.new_empty((b, h, 1), dtype=torch.float32)
 
 
+@torch.library.custom_op("fa_b200::decode_gqa", mutates_args=())
+def decode_gqa(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, scale: float,
+               seq_lens: torch.Tensor | None = None,
+               block_table: torch.Tensor | None = None) -> tuple[torch.Tensor, torch.Tensor]:
+    """Grouped-query attention of new tokens over a KV cache (``fa_decode_gqa``).
+
+    q ``[B, T, Hq, D]`` (the T tokens are the last T cache entries of each sequence; token t sees keys
+    up to its own position).  Cache, not paged: ``[B, Skv, Hkv, D]``; paged (``block_table`` int32
+    ``[B, max_pages]``): page pools ``[P, page_size, Hkv, D]``.  ``seq_lens`` int32 ``[B]`` optional.
+    Returns (O ``[B, T, Hq, D]``, LSE ``[B, T, Hq]``)."""
+    if q.dtype not in _DTYPES or k_cache.dtype != q.dtype or v_cache.dtype != q.dtype:
+        raise TypeError("fa_b200::decode_gqa: q and the cache must share dtype float16 or bfloat16")
+    if not (q.is_cuda and k_cache.is_cuda and v_cache.is_cuda):
+        raise RuntimeError("fa_b200: tensors must be on a CUDA device (there is no CPU path)")
+    if q.dim() != 4 or k_cache.dim() != 4 or v_cache.shape != k_cache.shape:
+        raise ValueError("fa_b200::decode_gqa: expected q [B,T,Hq,D] and 4-D caches of equal shape")
+    b, t, hq, d = q.shape
+    q, k_cache, v_cache = q.contiguous(), k_cache.contiguous(), v_cache.contiguous()
+    hkv = k_cache.shape[2]
+    kw = {}
+    if block_table is None:
+        if k_cache.shape[0] != b:
+            raise ValueError("fa_b200::decode_gqa: cache batch differs from q")
+        skv = k_cache.shape[1]
+        kw["kv_strides"] = (skv * hkv * d, d, hkv * d)
+    else:
+        n_pages, page = k_cache.shape[0], k_cache.shape[1]
+        block_table = block_table.to(torch.int32).contiguous()
+        skv = block_table.shape[1] * page
+        kw.update(kv_strides=(0, d, hkv * d), block_table=block_table, block_table_stride=block_table.shape[1],
+                  page_size=page, num_pages=n_pages, kv_page_stride=page * hkv * d)
+    if seq_lens is not None:
+        kw["seq_lens"] = seq_lens.to(torch.int32).contiguous()
+    o = torch.empty_like(q)
+    lse = torch.empty((b, t, hq), device=q.device, dtype=torch.float32)
+    with torch.cuda.device(q.device):
+        group = hq // hkv
+        n_qt = -(-t // max(1, min(t, 128 // group)))
+        splits = _fa.decode_gqa_default_splits(b * n_qt, hkv, skv)
+        ws_bytes = _fa.decode_workspace_bytes(b, t * hq, d, splits)
+        ws = torch.empty(ws_bytes, device=q.device, dtype=torch.uint8)
+        _fa.decode_gqa(q, k_cache, v_cache, o, lse, b, hq, hkv, skv, d, float(scale), dtype=_DTYPES[q.dtype],
+                       num_splits=splits, num_q_tokens=t, workspace=ws, workspace_bytes=ws_bytes,
+                       stream=torch.cuda.current_stream(q.device), **kw)
+    return o, lse
+
+
+@decode_gqa.register_fake
+def _(q, k_cache, v_cache, scale, seq_lens=None, block_table=None):
+    b, t, hq, _ = q.shape
+    return torch.empty_like(q), q.new_empty((b, t, hq), dtype=torch.float32)
+
+
 def sdpa(query: torch.Tensor, key: torch.Tensor, value: torch.Tensor, attn_mask=None,
          dropout_p: float = 0.0, is_causal: bool = False, scale: float | None = None) -> torch.Tensor:
     """``scaled_dot_product_attention`` for the cases the library covers (no mask, no dropout).
@@ -144,4 +197,4 @@ def sdpa(query: torch.Tensor, key: torch.Tensor, value: torch.Tensor, attn_mask=
     raise NotImplementedError("fa_b200.sdpa: only self-attention and single-row decode are covered")
 
 
-__all__ = ["prefill", "prefill_backward", "decode", "sdpa", "FaError"]
+__all__ = ["prefill", "prefill_backward", "decode", "decode_gqa", "sdpa", "FaError"]

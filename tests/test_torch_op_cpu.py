@@ -5,7 +5,7 @@ import torch
 def test_ops_registered_and_fake_shapes(fa):
     import __graft_entry__ as ge
     ge.load_module("torch_op")
-    assert all(hasattr(torch.ops.fa_b200, n) for n in ("prefill", "decode", "prefill_backward"))
+    assert all(hasattr(torch.ops.fa_b200, n) for n in ("prefill", "decode", "decode_gqa", "prefill_backward"))
     from torch._subclasses.fake_tensor import FakeTensorMode
     with FakeTensorMode():
         q = torch.empty((2, 3, 40, 64), dtype=torch.float16)

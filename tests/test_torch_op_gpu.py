@@ -63,3 +63,33 @@ def test_autograd_through_sdpa(op, dev):
         assert x.grad is not None and x.grad.dtype == torch.float16
         err = (x.grad.float().cpu() - r.grad).abs().max().item()
         assert err < 4e-3 * r.grad.abs().max().item() + 2e-3
+
+
+def test_decode_gqa_op_with_paged_cache(op, dev):
+    """torch.ops.fa_b200.decode_gqa on a paged cache against SDPA in fp32 on the CPU, per sequence."""
+    g = torch.Generator().manual_seed(9)
+    b, t, hq, hkv, d, page, lens = 2, 3, 8, 2, 128, 64, [500, 130]
+    pages_per_seq = 8
+    q = torch.randn((b, t, hq, d), generator=g).half()
+    k = torch.randn((b, pages_per_seq * page, hkv, d), generator=g).half()
+    v = torch.randn((b, pages_per_seq * page, hkv, d), generator=g).half()
+    n_pages = b * pages_per_seq + 2
+    perm = torch.randperm(n_pages, generator=g)[: b * pages_per_seq].view(b, pages_per_seq)
+    kp = torch.full((n_pages, page, hkv, d), float("nan"), dtype=torch.float16)
+    vp = torch.full((n_pages, page, hkv, d), float("nan"), dtype=torch.float16)
+    for i in range(b):
+        for pg in range(pages_per_seq):
+            r0 = pg * page
+            n = max(0, min(page, lens[i] - r0))
+            kp[perm[i, pg], :n] = k[i, r0:r0 + n]
+            vp[perm[i, pg], :n] = v[i, r0:r0 + n]
+    o, lse = torch.ops.fa_b200.decode_gqa(q.to(dev), kp.to(dev), vp.to(dev), d ** -0.5,
+                                          torch.tensor(lens, dtype=torch.int32, device=dev), perm.to(torch.int32).to(dev))
+    assert o.shape == q.shape and lse.shape == (b, t, hq)
+    for i in range(b):
+        for tt in range(t):
+            vis = lens[i] - t + tt + 1
+            kk = k[i, :vis].permute(1, 0, 2).repeat_interleave(hq // hkv, 0).float()      # [Hq, vis, D]
+            vv = v[i, :vis].permute(1, 0, 2).repeat_interleave(hq // hkv, 0).float()
+            ref = torch.nn.functional.scaled_dot_product_attention(q[i, tt].float()[:, None], kk, vv)[:, 0]
+            assert (o[i, tt].float().cpu() - ref).abs().max().item() < 2e-3
