@@ -171,7 +171,29 @@ bwd_kernel(const __grid_constant__ CUtensorMap ta0, const __grid_constant__ CUte
         fence_mbar_init();
     }
     __syncthreads();
-    if (warp == kCtlWarp) tmem_alloc(smem_u32(&tmem_slot), 512);
+    // streamed tiles of step t into stage t % kStages
+    auto load_step = [&](int t) {
+        const int s = t % kStages;
+        const uint32_t dst = b_s + s * 2 * L::kTileB;
+        mbar_arrive_expect_tx(smem_u32(&bar_full[s]), 2 * L::kTileB);
+        for (int b = 0; b < NBOX; b++) {
+            tma_load_3d(dst + b * L::kBoxB, &tb0, smem_u32(&bar_full[s]), b * 64, row0 + t * kW, bh);
+            tma_load_3d(dst + L::kTileB + b * L::kBoxB, &tb1, smem_u32(&bar_full[s]), b * 64, row0 + t * kW, bh);
+        }
+    };
+    if (warp == kCtlWarp) {
+        // the first loads go out before the TMEM allocation, so their latency overlaps it
+        if (lane == 0) {
+            mbar_arrive_expect_tx(smem_u32(&bar_a), 2 * L::kTile);
+            for (int b = 0; b < NBOX; b++) {
+                tma_load_3d(a0_s + b * L::kBox, &ta0, smem_u32(&bar_a), b * 64, tile * kT, bh);
+                tma_load_3d(a1_s + b * L::kBox, &ta1, smem_u32(&bar_a), b * 64, tile * kT, bh);
+            }
+            for (int t = 0; t < kStages && t < n_steps; t++) load_step(t);
+        }
+        __syncwarp();
+        tmem_alloc(smem_u32(&tmem_slot), 512);
+    }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -183,20 +205,6 @@ bwd_kernel(const __grid_constant__ CUtensorMap ta0, const __grid_constant__ CUte
             constexpr uint32_t idesc_t = make_idesc(kT, kW, FMT, FMT, kMajorK, kMajorK);
             constexpr uint64_t hi_k = make_sdesc_hi(16, 1024);
 
-            mbar_arrive_expect_tx(smem_u32(&bar_a), 2 * L::kTile);
-            for (int b = 0; b < NBOX; b++) {
-                tma_load_3d(a0_s + b * L::kBox, &ta0, smem_u32(&bar_a), b * 64, tile * kT, bh);
-                tma_load_3d(a1_s + b * L::kBox, &ta1, smem_u32(&bar_a), b * 64, tile * kT, bh);
-            }
-            auto load_step = [&](int t) {
-                const int s = t % kStages;
-                const uint32_t dst = b_s + s * 2 * L::kTileB;
-                mbar_arrive_expect_tx(smem_u32(&bar_full[s]), 2 * L::kTileB);
-                for (int b = 0; b < NBOX; b++) {
-                    tma_load_3d(dst + b * L::kBoxB, &tb0, smem_u32(&bar_full[s]), b * 64, row0 + t * kW, bh);
-                    tma_load_3d(dst + L::kTileB + b * L::kBoxB, &tb1, smem_u32(&bar_full[s]), b * 64, row0 + t * kW, bh);
-                }
-            };
             // products of step t into buffer t & 1: T0 = A0 B0^T, T1 = A1 B1^T (kW columns each)
             auto issue_products = [&](int t) -> bool {
                 const int s = t % kStages;
@@ -217,7 +225,6 @@ bwd_kernel(const __grid_constant__ CUtensorMap ta0, const __grid_constant__ CUte
                 tc_commit(smem_u32(&bar_t[t & 1]));
                 return true;
             };
-            for (int t = 0; t < kStages && t < n_steps; t++) load_step(t);
             bool ok = mbar_wait(smem_u32(&bar_a), 0, ctl, kBwdBarA);
             for (int t = 0; ok && t < n_steps; t++) {
                 if (t >= 2) {
