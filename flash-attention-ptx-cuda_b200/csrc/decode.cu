@@ -502,6 +502,7 @@ FA_EXPORT int fa_decode_gqa(const fa_decode_gqa_args* a) {
     g.n_tok = n_tok;
     g.q = a->q; g.k = a->k; g.v = a->v;
     g.o_part = o_part; g.lse_part = lse_part;
+    g.o_final = a->o; g.lse_final = a->lse;
     g.batch = a->batch_size; g.n_kv_heads = a->num_kv_heads; g.group = group;
     g.kv_len = a->seq_len_kv; g.d_head = a->d_head; g.dtype = a->dtype;
     g.n_splits = splits; g.tiles_per_split = tps;
@@ -513,6 +514,7 @@ FA_EXPORT int fa_decode_gqa(const fa_decode_gqa_args* a) {
     g.scale = a->scale; g.stream = stream;
     int rc = launch_decode_gqa(g, st);
     if (rc != FA_OK) return rc;
+    if (splits == 1) return FA_OK;                      // the kernel wrote o and lse itself
     return launch_combine(o_part, lse_part, splits, a->d_head, (long long)splits * a->d_head, 1, splits,
                           (int)rows, a->d_head, a->o, a->lse, nullptr, e4m3 ? FA_DTYPE_BF16 : a->dtype, stream);
 }

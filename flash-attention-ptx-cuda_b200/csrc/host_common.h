@@ -70,7 +70,8 @@ int launch_prefill_fp8(const fa_prefill_args& a, DeviceState* st);
 // in the rows of one query tile; work items are (batch x KV head, KV split).
 struct GqaLaunch {
     const void* q; const void* k; const void* v;
-    float* o_part; float* lse_part;           // [row][split][D] and [row][split], row = b * Hq + hq
+    float* o_part; float* lse_part;           // [row][split][D] and [row][split], row = (b * T + t) * Hq + hq
+    void* o_final; float* lse_final;          // the caller's o / lse: written directly when n_splits == 1
     int batch, n_kv_heads, group, kv_len, d_head, dtype;
     int n_tok;                                // query tokens per sequence (1 = plain decode)
     int n_splits, tiles_per_split;

@@ -141,6 +141,8 @@ struct PrefillSmem {
 struct GqaDev {
     float* o_part;          // [row][split][D] fp32, row = (batch x KV head) * group + query head in group
     float* lse_part;        // [row][split]
+    uint16_t* o_final;      // with one split the epilogue writes the 16-bit result and its LSE directly
+    float* lse_final;       // (may be null)
     int n_splits, tiles_per_split, group, n_hkv;
     int n_tok;              // query tokens per sequence
     int tok_per_tile;       // tokens per query tile (row r of a tile: token r / group, head r % group)
@@ -175,8 +177,10 @@ __device__ __forceinline__ bool get_item(int k, int n_items, int n_bh, int n_qti
         if (idx >= n_items) return false;
         const int bq = idx / gq.n_splits;             // (batch x KV head, query tile)
         it.split = idx - bq * gq.n_splits;
-        it.bh = bq / gq.n_qt;
-        it.tok0 = (bq - it.bh * gq.n_qt) * gq.tok_per_tile;
+        // the later query tiles see more keys: all heads' last tiles first
+        const int qt_rev = bq / n_bh;
+        it.bh = bq - qt_rev * n_bh;
+        it.tok0 = (gq.n_qt - 1 - qt_rev) * gq.tok_per_tile;
         it.t0 = it.split * gq.tiles_per_split;
         it.kv_len = gq.seq_lens ? min(seq_len, max(0, __ldg(gq.seq_lens + it.bh / gq.n_hkv))) : seq_len;
         // keys the tile's last token sees (the query tokens are the last n_tok entries of the cache)
@@ -522,9 +526,15 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                     // a KV split past the end of a short sequence: weight zero in the merge
                     if (it.empty && r_in_tile < gq.live_rows && it.tok0 + r_in_tile / gq.group < gq.n_tok) {
                         const size_t pidx = gqa_partial_index(gq, it, r_in_tile);
-                        gq.lse_part[pidx] = -INFINITY;
-                        float4* dst = reinterpret_cast<float4*>(gq.o_part + pidx * D);
-                        for (int e = 0; e < D / 4; e++) dst[e] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                        if (gq.n_splits == 1) {               // the only split of a sequence without keys: O = 0
+                            uint4* dst = reinterpret_cast<uint4*>(gq.o_final + pidx * D);
+                            for (int e = 0; e < D / 8; e++) dst[e] = make_uint4(0u, 0u, 0u, 0u);
+                            if (gq.lse_final != nullptr) gq.lse_final[pidx] = -INFINITY;
+                        } else {
+                            gq.lse_part[pidx] = -INFINITY;
+                            float4* dst = reinterpret_cast<float4*>(gq.o_part + pidx * D);
+                            for (int e = 0; e < D / 4; e++) dst[e] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                        }
                     }
                 }
                 continue;
@@ -588,7 +598,12 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                 // a token with no visible key (a sequence shorter than the token count): O = 0, LSE = -inf
                 const bool seen = l_run > 0.0f;
                 if (!seen) inv_l = 0.0f;
-                if (live) gq.lse_part[pidx] = seen ? kLn2 * (m_fin + log2f(l_run)) : -INFINITY;
+                const bool direct = gq.n_splits == 1;     // nothing to merge: this is the result
+                const float lse_val = seen ? kLn2 * (m_fin + log2f(l_run)) : -INFINITY;
+                if (live) {
+                    if (!direct) gq.lse_part[pidx] = lse_val;
+                    else if (gq.lse_final != nullptr) gq.lse_final[pidx] = lse_val;
+                }
 #pragma unroll 1
                 for (int c = 0; c < D / 32; c++) {
                     uint32_t o[32];
@@ -598,7 +613,20 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                         __syncwarp();
                         if (lane == 0) mbar_arrive(smem_u32(&bar_ofree));
                     }
-                    if (live) {
+                    if (!seen) {                          // P was 2^(-inf + inf) there: not a number
+#pragma unroll
+                        for (int i = 0; i < 32; i++) o[i] = 0u;
+                    }
+                    if (live && direct) {
+                        uint4* dst = reinterpret_cast<uint4*>(gq.o_final + pidx * D + c * 32);
+#pragma unroll
+                        for (int e = 0; e < 4; e++)
+                            dst[e] = make_uint4(
+                                pack_16<BF16>(__uint_as_float(o[8 * e]) * inv_l, __uint_as_float(o[8 * e + 1]) * inv_l),
+                                pack_16<BF16>(__uint_as_float(o[8 * e + 2]) * inv_l, __uint_as_float(o[8 * e + 3]) * inv_l),
+                                pack_16<BF16>(__uint_as_float(o[8 * e + 4]) * inv_l, __uint_as_float(o[8 * e + 5]) * inv_l),
+                                pack_16<BF16>(__uint_as_float(o[8 * e + 6]) * inv_l, __uint_as_float(o[8 * e + 7]) * inv_l));
+                    } else if (live) {
                         float4* dst = reinterpret_cast<float4*>(gq.o_part + pidx * D + c * 32);
 #pragma unroll
                         for (int e = 0; e < 8; e++)
@@ -873,7 +901,8 @@ int launch_gqa_instance(const GqaLaunch& g, DeviceState* st, const CUtensorMap& 
     const unsigned grid = (unsigned)(n_items < st->sm_count ? n_items : st->sm_count);
     int page_shift = 0;
     while ((1 << page_shift) < g.page_size) page_shift++;
-    const GqaDev gq{g.o_part, g.lse_part, g.n_splits, g.tiles_per_split, g.group, g.n_kv_heads,
+    const GqaDev gq{g.o_part, g.lse_part, static_cast<uint16_t*>(g.o_final), g.lse_final, g.n_splits,
+                    g.tiles_per_split, g.group, g.n_kv_heads,
                     g.n_tok, tok_per_tile, n_qt, tok_per_tile * g.group, g.seq_lens, g.block_table, g.table_stride,
                     page_shift};
     kernel<<<grid, kThreads, L::kTotal, g.stream>>>(tq, tk, tv, tq, nullptr, g.kv_len, n_bh, 1, (int)n_items,
