@@ -139,7 +139,7 @@ struct PrefillSmem {
 
 // Grouped-query decode mode (device side of GqaLaunch).
 struct GqaDev {
-    float* o_part;          // [row][split][D] fp32, row = (batch x KV head) * group + query head in group
+    float* o_part;          // [row][split][D] fp32, row = (batch * n_tok + token) * Hq + query head
     float* lse_part;        // [row][split]
     uint16_t* o_final;      // with one split the epilogue writes the 16-bit result and its LSE directly
     float* lse_final;       // (may be null)
@@ -155,7 +155,8 @@ struct GqaDev {
 };
 
 // Work list: item index -> (query tile, head), heaviest first when causal.  In grouped-query
-// decode mode an item is (batch x KV head, KV split): key tiles [t0, t0 + n_kv) of that head.
+// decode mode an item is (batch x KV head, query tile, KV split): key tiles [t0, t0 + n_kv) of that
+// head for the tokens from tok0 on.
 struct Item { int q_start, bh, n_kv, t0, split, kv_len, tok0; bool empty; };
 
 // Index of the partial result of tile row r: output row ((batch * n_tok + token) * Hq + query head),
@@ -591,8 +592,9 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&bar_odone), it_n & 1, ctl, kBarODone))) break;
             tc_fence_after();
             if constexpr (GQA) {
-                // Partial result of this KV split: normalised fp32 O and its LSE for the rows that
-                // carry a query head; the merge over splits is a separate kernel.
+                // Result of this KV split for the rows that carry a (token, head) pair: with several
+                // splits a normalised fp32 partial O and its LSE (the merge is a separate kernel), with
+                // one split the final 16-bit O and the LSE.
                 const bool live = r_in_tile < gq.live_rows && it.tok0 + r_in_tile / gq.group < gq.n_tok;
                 const size_t pidx = gqa_partial_index(gq, it, r_in_tile);
                 // a token with no visible key (a sequence shorter than the token count): O = 0, LSE = -inf
