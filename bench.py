@@ -529,6 +529,30 @@ def run_other_configs(fa, torch, dev, stream, peaks, gqa_batch=0):
             "algorithmic_bytes": algo, "tokens_per_s": b / (ms * 1e-3)}
         del kc, vc, ws
 
+    # the same entry point with several query tokens per sequence: a whole causal GQA prefill as one
+    # chunk (tensor-bound: TFLOP/s on the causal count), and 4 speculative tokens per sequence (HBM-bound)
+    for (b, hq, hkv, skv, d, t) in ((8, 32, 8, 2048, 128, 2048), (gb, 32, 8, 16384, 128, 4)):
+        kc = torch.randn((b, skv, hkv, d), device=dev, dtype=torch.float32).to(torch.float16)
+        vc = torch.randn((b, skv, hkv, d), device=dev, dtype=torch.float32).to(torch.float16)
+        qg = torch.randn((b, t, hq, d), device=dev, dtype=torch.float32).to(torch.float16)
+        og = torch.empty_like(qg)
+        lg = torch.empty((b, t, hq), device=dev, dtype=torch.float32)
+        tpt = min(t, 128 // (hq // hkv))
+        splits = fa.decode_gqa_default_splits(b * (-(-t // tpt)), hkv, skv)
+        wsb = fa.decode_workspace_bytes(b, t * hq, d, splits)
+        ws = torch.empty(wsb, device=dev, dtype=torch.uint8)
+        sc_g = float(1.0 / np.sqrt(d))
+        ms = timed(lambda: fa.decode_gqa(qg, kc, vc, og, lg, b, hq, hkv, skv, d, sc_g, dtype="f16", num_q_tokens=t,
+                                         num_splits=splits, kv_strides=(skv * hkv * d, d, hkv * d), workspace=ws,
+                                         workspace_bytes=wsb, stream=stream))
+        keys = sum(skv - t + i + 1 for i in range(t))
+        tf = 4.0 * d * b * hq * keys / (ms * 1e-3) / 1e12
+        algo = 2 * b * hkv * skv * d * 2 + 2 * b * t * hq * d * 2
+        out[f"chunk_f16_b{b}_hq{hq}_hkv{hkv}_skv{skv}_d{d}_t{t}"] = {
+            "ms": ms, "tflops": tf, "GBps_cache": algo / (ms * 1e-3) / 1e9, "splits": splits,
+            "note": "fa_decode_gqa with num_q_tokens = t, causal among the new tokens"}
+        del kc, vc, ws
+
     # the same decode over an e4m3 cache (one byte per element; Q e4m3 as well, per-(batch, KV head) scales)
     b, hq, hkv, skv, d = gb, 32, 8, 16384, 128
     kc8 = torch.randn((b, skv, hkv, d), device=dev, dtype=torch.float32).to(torch.float8_e4m3fn).view(torch.uint8)
