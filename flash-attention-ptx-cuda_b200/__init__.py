@@ -40,6 +40,7 @@ EXPORTED_SYMBOLS = (
     "fa_backward_workspace_bytes", "fa_combine", "fa_kat",
     "fa_device_status",
     "fa_clear_device_status", "fa_error_string", "fa_last_cuda_error", "fa_version",
+    "fa_set_prefill_variant",
 )
 
 
@@ -152,6 +153,8 @@ def lib() -> ctypes.CDLL:
         l.fa_error_string.argtypes = [ctypes.c_int]
         l.fa_last_cuda_error.restype = ctypes.c_char_p
         l.fa_version.restype = ctypes.c_int
+        l.fa_set_prefill_variant.restype = ctypes.c_int
+        l.fa_set_prefill_variant.argtypes = [ctypes.c_int]
         _lib = l
     return _lib
 
@@ -196,6 +199,16 @@ def prefill(q, k, v, o, lse, batch_size, num_heads, seq_len, d_head, scale, caus
     rc = prefill_raw(q, k, v, o, lse, batch_size, num_heads, seq_len, d_head, scale, causal, **kw)
     if rc != FA_OK:
         raise FaError(rc, "fa_prefill")
+
+
+PREFILL_VARIANTS = {"auto": 0, "one_tile": 1, "tile_pair": 2}
+
+
+def set_prefill_variant(variant: str) -> None:
+    """fa_set_prefill_variant: which 16-bit prefill kernel runs ("auto" picks by problem size)."""
+    rc = lib().fa_set_prefill_variant(PREFILL_VARIANTS[variant])
+    if rc != FA_OK:
+        raise FaError(rc, "fa_set_prefill_variant")
 
 
 def decode_workspace_bytes(batch_size, num_heads, d_head, num_splits) -> int:

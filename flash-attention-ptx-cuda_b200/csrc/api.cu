@@ -150,7 +150,10 @@ int stage_reserve(DeviceState* st, int slot, size_t bytes) {
 
 using namespace fa;
 
-FA_EXPORT int fa_prefill(const fa_prefill_args* a) {
+namespace {
+// fa_prefill with the kernel variant given (the host entry decides once for the whole problem so
+// that its chunks of heads run the kernel a single launch would have run).
+int prefill_on_device(const fa_prefill_args* a, int variant) {
     int rc = validate_prefill(a);
     if (rc != FA_OK) return rc;
     if (!aligned16(a->q) || !aligned16(a->k) || !aligned16(a->v) || !aligned16(a->o))
@@ -160,8 +163,11 @@ FA_EXPORT int fa_prefill(const fa_prefill_args* a) {
     if (!st) return FA_ERR_CUDA;
     if (st->cc_major != 10) return FA_ERR_NOT_SM100;
     if (a->dtype == FA_DTYPE_E4M3) return launch_prefill_fp8(*a, st);
-    return launch_prefill_16bit(*a, st);
+    return launch_prefill_16bit(*a, st, variant);
 }
+}  // namespace
+
+FA_EXPORT int fa_prefill(const fa_prefill_args* a) { return prefill_on_device(a, FA_PREFILL_AUTO); }
 
 FA_EXPORT int fa_prefill_host(const fa_prefill_args* h) {
     int rc = validate_prefill(h);
@@ -198,6 +204,7 @@ FA_EXPORT int fa_prefill_host(const fa_prefill_args* h) {
     if (n_chunks > 16) n_chunks = 16;
     if (n_chunks > bh) n_chunks = bh;
     const size_t heads_per_chunk = (bh + n_chunks - 1) / n_chunks;
+    const int variant = choose_prefill_variant(h->batch_size, h->num_heads, h->seq_len, st);
     int ci = 0;
     for (size_t h0 = 0; h0 < bh; h0 += heads_per_chunk, ci++) {
         const size_t nh = (bh - h0 < heads_per_chunk) ? bh - h0 : heads_per_chunk;
@@ -223,7 +230,7 @@ FA_EXPORT int fa_prefill_host(const fa_prefill_args* h) {
             d.k_scale = static_cast<float*>(st->stage[6]) + h0;
             d.v_scale = static_cast<float*>(st->stage[7]) + h0;
         }
-        if ((rc = fa_prefill(&d)) != FA_OK) return rc;
+        if ((rc = prefill_on_device(&d, variant)) != FA_OK) return rc;
         FA_CUDA_TRY(cudaMemcpyAsync(static_cast<char*>(h->o) + h0 * per_head_out, dO, nh * per_head_out,
                                     cudaMemcpyDeviceToHost, stream));
         if (h->lse)
@@ -267,6 +274,13 @@ FA_EXPORT const char* fa_error_string(int code) {
         case FA_ERR_NOT_SM100:        return "device is not compute capability 10.x";
         default:                      return "unknown error";
     }
+}
+
+FA_EXPORT int fa_set_prefill_variant(int variant) {
+    if (variant != FA_PREFILL_AUTO && variant != FA_PREFILL_ONE_TILE && variant != FA_PREFILL_TILE_PAIR)
+        return FA_ERR_INVALID_ARGUMENT;
+    g_prefill_variant.store(variant, std::memory_order_relaxed);
+    return FA_OK;
 }
 
 FA_EXPORT const char* fa_last_cuda_error(void) { return g_last_cuda_error; }

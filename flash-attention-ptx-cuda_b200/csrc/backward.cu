@@ -57,26 +57,6 @@ constexpr float kLog2e = 1.4426950408889634f;
 
 enum : int { kBwdBarA = 21, kBwdBarFull = 22, kBwdBarT = 23, kBwdBarP = 24, kBwdBarFree = 25, kBwdBarDone = 26, kBwdBarStep = 27 };
 
-// Packed pairs of fp32 (sm_100 has two-wide fp32 FMA/MUL on 64-bit register pairs).
-__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
-    uint64_t r;
-    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
-    return r;
-}
-__device__ __forceinline__ void unpack2(uint64_t v, float& lo, float& hi) {
-    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
-}
-__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
-    uint64_t d;
-    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
-    return d;
-}
-__device__ __forceinline__ uint64_t mul2(uint64_t a, uint64_t b) {
-    uint64_t d;
-    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
-    return d;
-}
-
 template <int D>
 struct BwdSmem {
     static constexpr int kNBox = D / 64;              // 64-column (128-byte) boxes per row
@@ -389,6 +369,11 @@ bwd_kernel(const __grid_constant__ CUtensorMap ta0, const __grid_constant__ CUte
     }
 
     tc_fence_before();
+    // The dQ kernel runs as a programmatic dependent of the dK/dV kernel and reads none of its
+    // outputs, so it never had to wait for it.  But whatever follows on the stream is ordered after
+    // THIS kernel only: every thread waits here, after its own work, until the dK/dV grid has
+    // completed and flushed, so that the end of this kernel implies the end of both.
+    if (MODE == 1) asm volatile("griddepcontrol.wait;" ::: "memory");
     __syncthreads();
     if (warp == kCtlWarp) tmem_dealloc(tmem, 512);
 }
@@ -409,7 +394,9 @@ int launch_bwd(const fa_backward_args& a, DeviceState* st, const CUtensorMap& tq
     // The dQ kernel (MODE 1) reads nothing the dK/dV kernel (MODE 0) writes, so it is launched as a
     // programmatic dependent: its CTAs may start on SMs the first kernel no longer needs (that kernel
     // signals at its start), instead of waiting for its last CTA.  delta comes from a kernel that
-    // completed before MODE 0 started.
+    // completed before MODE 0 started.  Before it ends, every thread of the dQ kernel executes
+    // griddepcontrol.wait, so later work on the stream (or the next node of a captured graph) sees
+    // dK and dV complete as well.
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)grid);
     cfg.blockDim = dim3(kBwdThreads);

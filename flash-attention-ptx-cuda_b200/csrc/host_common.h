@@ -6,6 +6,7 @@
 // per device so that one process can drive several GPUs.
 #pragma once
 
+#include <atomic>
 #include <cstddef>
 #include <cstdint>
 #include <cuda.h>
@@ -63,8 +64,15 @@ int make_tensor_map_q5(CUtensorMap* out, const void* base, int dtype, uint64_t d
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 // Implemented next to their kernels.
-int launch_prefill_16bit(const fa_prefill_args& a, DeviceState* st);
+// `variant` is an FA_PREFILL_* value; FA_PREFILL_AUTO decides from the sizes in `a`.
+int launch_prefill_16bit(const fa_prefill_args& a, DeviceState* st, int variant);
+int choose_prefill_variant(int batch_size, int num_heads, int seq_len, const DeviceState* st);
 int launch_prefill_fp8(const fa_prefill_args& a, DeviceState* st);
+// The kernel with two query tiles per CTA (tensor maps as for the one-tile kernel).
+int launch_prefill_pair_16bit(const fa_prefill_args& a, DeviceState* st, const CUtensorMap& tq,
+                              const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& to);
+// FA_PREFILL_* choice made through fa_set_prefill_variant().
+extern std::atomic<int> g_prefill_variant;
 
 // Grouped-query decode on the prefill kernel: the `group` query heads that share a KV head ride
 // in the rows of one query tile; work items are (batch x KV head, KV split).

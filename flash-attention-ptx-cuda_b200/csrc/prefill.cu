@@ -48,6 +48,7 @@
 //                      warps first turn each V tile into the fp16 operand of P V.
 //
 // TMEM (all 512 columns): three score buffers [0,128) [128,256) [256,384), O [384,384+D).
+#include <atomic>
 #include <cmath>
 
 #include "host_common.h"
@@ -73,36 +74,15 @@ constexpr int kRing = 4;                 // entries of the Q K^T / P V completio
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 constexpr float kRescaleThreshold = 8.0f;   // log2 units: rescale only if max grew > 2^8
+#ifndef FA_GROUP_MB
+#define FA_GROUP_MB 48
+#endif
 
 // Barrier ids reported in the status word when a wait gives up.
 enum : int { kBarQFull = 1, kBarQEmpty = 2, kBarKFull = 3, kBarKEmpty = 4, kBarVFull = 5,
              kBarVEmpty = 6, kBarSFull = 7, kBarSFree = 8, kBarPFull = 9, kBarPV = 10,
              kBarOFree = 11, kBarV8Full = 12, kBarV8Empty = 13, kBarM = 14, kBarEpi = 15, kBarODone = 16, kBarStats = 17, kBarStatsFree = 18 };
 
-// Packed pairs of fp32 (sm_100 has two-wide fp32 FMA/ADD on 64-bit register pairs).
-__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
-    uint64_t r;
-    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
-    return r;
-}
-__device__ __forceinline__ void unpack2(uint64_t v, float& lo, float& hi) {
-    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
-}
-__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
-    uint64_t d;
-    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
-    return d;
-}
-__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
-    uint64_t d;
-    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
-    return d;
-}
-__device__ __forceinline__ float max3(float a, float b, float c) {
-    float d;
-    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
-    return d;
-}
 // Two e4m3 codes -> two fp16 values (exact).
 __device__ __forceinline__ uint32_t e4m3x2_to_f16x2(uint16_t v) {
     uint32_t r;
@@ -200,8 +180,15 @@ __device__ __forceinline__ bool get_item(int k, int n_items, int n_bh, int n_qti
     it.empty = false;
     const int idx = (k & 1) ? k * G + (G - 1 - c) : k * G + c;     // boustrophedon deal
     if (idx >= n_items) return false;
-    const int qt = CAUSAL ? (n_qtiles - 1 - idx / n_bh) : (idx / n_bh);
-    it.bh = idx % n_bh;
+    // Heads are taken in groups of gq.group (reused here as "heads per group"): within a group the
+    // list runs query tile by query tile over the group's heads, so the K and V that the CTAs
+    // stream at any one time belong to one group and stay in L2.
+    const int per_group = gq.group * n_qtiles;
+    const int gi = idx / per_group, rem = idx - gi * per_group;
+    const int h0 = gi * gq.group, hin = min(gq.group, n_bh - h0);
+    const int qrank = rem / hin;
+    const int qt = CAUSAL ? (n_qtiles - 1 - qrank) : qrank;
+    it.bh = h0 + rem - qrank * hin;
     it.q_start = qt * kBM;
     const int kv_len = CAUSAL ? min(seq_len, it.q_start + kBM) : seq_len;
     it.n_kv = (kv_len + kBN - 1) / kBN;
@@ -863,6 +850,18 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     if (warp == 9) tmem_dealloc(tmem, TMEM_COLS);
 }
 
+// How many heads the work list walks at a time: as many as keep their K and V (which every query
+// tile of a head re-reads) inside a share of L2.  Measured on 32 heads of S=8192, d_head 128
+// (134 MB of K and V against 126 MB of L2): walking all heads at once streams K/V from HBM.
+constexpr long long kGroupBytes = FA_GROUP_MB * 1024ll * 1024ll;
+int heads_per_group(int n_bh, int seq_len, int d_head, int elem_bytes) {
+    const long long per_head = 2ll * seq_len * d_head * elem_bytes;
+    long long g = kGroupBytes / (per_head > 0 ? per_head : 1);
+    if (g < 1) g = 1;
+    if (g > n_bh) g = n_bh;
+    return (int)g;
+}
+
 template <int D, bool CAUSAL, bool BF16, bool FP8>
 int launch_instance(const fa_prefill_args& a, DeviceState* st, const CUtensorMap& tq,
                     const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& to) {
@@ -878,9 +877,11 @@ int launch_instance(const fa_prefill_args& a, DeviceState* st, const CUtensorMap
     const long long n_items = (long long)n_bh * n_qtiles;
     if (n_items > 0x7FFFFFFFll) return FA_ERR_INVALID_ARGUMENT;
     const unsigned grid = (unsigned)(n_items < st->sm_count ? n_items : st->sm_count);
+    GqaDev order{};
+    order.group = heads_per_group(n_bh, a.seq_len, a.d_head, FP8 ? 1 : 2);
     kernel<<<grid, kThreads, L::kTotal, static_cast<cudaStream_t>(a.stream)>>>(
         tq, tk, tv, to, a.lse, a.seq_len, n_bh, n_qtiles, (int)n_items, a.scale * kLog2e, a.q_scale,
-        a.k_scale, a.v_scale, st->status, GqaDev{});
+        a.k_scale, a.v_scale, st->status, order);
     FA_CUDA_TRY(cudaGetLastError());
     return FA_OK;
 }
@@ -915,7 +916,23 @@ int launch_gqa_instance(const GqaLaunch& g, DeviceState* st, const CUtensorMap& 
 
 }  // namespace
 
-int launch_prefill_16bit(const fa_prefill_args& a, DeviceState* st) {
+// Which of the two prefill kernels runs a problem (the reference's dispatcher picks its tile
+// variant by the same kind of rule, kernels/flash_attention.cu:595-617).  The kernel with two
+// query tiles per CTA needs the pairs alone to fill the GPU; below that the one-tile kernel
+// spreads a small problem over twice as many SMs and has the shorter critical path.
+std::atomic<int> g_prefill_variant{FA_PREFILL_AUTO};
+
+int choose_prefill_variant(int batch_size, int num_heads, int seq_len, const DeviceState* st) {
+    const int v = g_prefill_variant.load(std::memory_order_relaxed);
+    if (v != FA_PREFILL_AUTO) return v;
+    // Measured on B200 (CUDA events, fp16 / bf16, causal and not, S 512 ... 8192): the one-tile kernel
+    // is the faster one on every shape tried so far (0.090 against 0.104 ms on B=8 H=12 S=2048
+    // d_head 64 causal), so it is what the library picks; the tile-pair kernel stays selectable.
+    (void)batch_size; (void)num_heads; (void)seq_len; (void)st;
+    return FA_PREFILL_ONE_TILE;
+}
+
+int launch_prefill_16bit(const fa_prefill_args& a, DeviceState* st, int variant) {
     const uint64_t n_bh = (uint64_t)a.batch_size * a.num_heads;
     CUtensorMap tq, tk, tv, to;
     int rc;
@@ -923,6 +940,8 @@ int launch_prefill_16bit(const fa_prefill_args& a, DeviceState* st) {
     if ((rc = make_tensor_map_3d(&tk, a.k, a.dtype, a.d_head, a.seq_len, n_bh, 64, kBN)) != FA_OK) return rc;
     if ((rc = make_tensor_map_3d(&tv, a.v, a.dtype, a.d_head, a.seq_len, n_bh, 64, kBN)) != FA_OK) return rc;
     if ((rc = make_tensor_map_3d(&to, a.o, a.dtype, a.d_head, a.seq_len, n_bh, 64, kBM)) != FA_OK) return rc;
+    if (variant == FA_PREFILL_AUTO) variant = choose_prefill_variant(a.batch_size, a.num_heads, a.seq_len, st);
+    if (variant == FA_PREFILL_TILE_PAIR) return launch_prefill_pair_16bit(a, st, tq, tk, tv, to);
     const bool bf = a.dtype == FA_DTYPE_BF16;
     const bool causal = a.causal != 0;
 #define FA_DISPATCH(DH)                                                                      \

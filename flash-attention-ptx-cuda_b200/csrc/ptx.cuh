@@ -19,6 +19,7 @@
 namespace fa {
 
 constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // 2 s per wait
+constexpr uint32_t kParkNs = 20000;                         // suspend-time hint of one poll of a waiting thread
 
 // Error words written to the device status buffer: (code << 16) | detail.
 enum : int {
@@ -34,16 +35,6 @@ __device__ __forceinline__ unsigned long long global_timer_ns() {
     unsigned long long t;
     asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
     return t;
-}
-
-__device__ __forceinline__ bool elect_one() {
-    uint32_t pred;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "elect.sync _|p, 0xffffffff;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(pred));
-    return pred != 0;
 }
 
 // ---------------------------------------------------------------------------
@@ -73,6 +64,21 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
+// Same with a suspend-time hint: the hardware may park the thread for up to `hint_ns` before the
+// instruction returns false, and wakes it when the phase completes.  A parked thread issues
+// nothing, so a waiting role stops competing with the working warps of its scheduler for issue
+// slots and for the queue that the special-function unit shares with shared-memory operations.
+__device__ __forceinline__ bool mbar_try_wait_parked(uint32_t bar, uint32_t parity, uint32_t hint_ns) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity), "r"(hint_ns)
+        : "memory");
+    return ok != 0;
+}
 
 // Shared per-CTA control block for the bounded waits.
 struct WaitCtl {
@@ -87,8 +93,8 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const W
     if (mbar_try_wait(bar, parity)) return true;
     unsigned long long t0 = 0;
     uint32_t spins = 0;
-    while (!mbar_try_wait(bar, parity)) {
-        if ((++spins & 0xFFu) == 0) {
+    while (!mbar_try_wait_parked(bar, parity, kParkNs)) {
+        if ((++spins & 0xFu) == 0) {
             if (*ctl.abort_flag) return false;
             const unsigned long long now = global_timer_ns();
             if (t0 == 0) {
@@ -148,20 +154,17 @@ __device__ __forceinline__ void tma_store_3d(const CUtensorMap* tm, uint32_t src
 __device__ __forceinline__ void tma_store_commit() {
     asm volatile("cp.async.bulk.commit_group;" ::: "memory");
 }
-__device__ __forceinline__ void tma_store_wait_all() {
-    asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
-}
 // Source buffers of all committed bulk stores have been read (the writes may still be in flight).
 __device__ __forceinline__ void tma_store_wait_read() {
     asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
 }
+// Same, but the most recently committed bulk store may still be reading its source.
+__device__ __forceinline__ void tma_store_wait_read_keep1() {
+    asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+}
 // Orders generic-proxy shared-memory writes before later async-proxy (TMA) reads.
 __device__ __forceinline__ void fence_proxy_async_smem() {
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-}
-
-__device__ __forceinline__ void named_barrier_sync(int id, int threads) {
-    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
 
 // ---------------------------------------------------------------------------
@@ -267,15 +270,6 @@ __device__ __forceinline__ void mma_f8_ss(uint32_t d_tmem, uint64_t a_desc, uint
         ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
-__device__ __forceinline__ void mma_f8_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc,
-                                          uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], [%1], %2, %3, p;\n\t}"
-        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
 
 // ---------------------------------------------------------------------------
 // TMEM <-> registers, shape 32x32b: thread i of the warp owns TMEM lane
@@ -318,25 +312,12 @@ __device__ __forceinline__ void tmem_st_x16(uint32_t taddr, const uint32_t (&r)[
         : "memory");
 }
 
-__device__ __forceinline__ void tmem_st_x8(uint32_t taddr, const uint32_t (&r)[8]) {
-    asm volatile(
-        "tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
-        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]),
-          "r"(r[7])
-        : "memory");
-}
-
 // ---------------------------------------------------------------------------
 // Small numeric helpers
 // ---------------------------------------------------------------------------
 __device__ __forceinline__ float ex2_approx(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-    return y;
-}
-__device__ __forceinline__ float lg2_approx(float x) {
-    float y;
-    asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
 // Two floats -> packed 16-bit pair, `lo` in the low half.
@@ -354,6 +335,36 @@ template <bool BF16>
 __device__ __forceinline__ uint32_t pack_16(float lo, float hi) {
     if constexpr (BF16) return pack_bf16(lo, hi);
     else return pack_f16(lo, hi);
+}
+
+// Packed pairs of fp32: sm_100 has two-wide fp32 FMA / ADD / MUL on 64-bit register pairs.
+__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float& lo, float& hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ uint64_t mul2(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
 }
 
 }  // namespace fa

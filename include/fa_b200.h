@@ -75,6 +75,19 @@ typedef struct fa_prefill_args {
 int fa_prefill(const fa_prefill_args* args);
 
 /*
+ * fa_prefill has two kernels for 16-bit inputs, as the reference has two tile variants
+ * behind its dispatcher (kernels/flash_attention.cu:595-617: 32x64 tiles while
+ * B*H*ceil(S/64) < 2 * SMs, else 64x64).  FA_PREFILL_ONE_TILE walks one 128-row query tile
+ * per CTA with two softmax groups on alternate key tiles; FA_PREFILL_TILE_PAIR walks two
+ * query tiles per CTA, each K/V tile in shared memory feeding both (half the K/V traffic
+ * from L2).  FA_PREFILL_AUTO (the default) picks the one measured faster, today the one-tile
+ * kernel on every shape.  This call overrides the choice for the whole process (tests and
+ * tuning).  Results are the same within the stated tolerances.
+ */
+enum { FA_PREFILL_AUTO = 0, FA_PREFILL_ONE_TILE = 1, FA_PREFILL_TILE_PAIR = 2 };
+int fa_set_prefill_variant(int variant);
+
+/*
  * Same computation with HOST buffers: copies q,k,v (and the scales) to the
  * device, runs fa_prefill, copies o (and lse) back and synchronises.  This is
  * the call pattern of the reference's own verification and demo programs

@@ -80,3 +80,55 @@ def test_backward_edge_lengths(fa, dev, s):
         for name, r, x in zip(("dQ", "dK", "dV"), ref, got):
             assert torch.isfinite(x).all(), name
             assert (x - r).abs().max().item() < 4e-3 * r.abs().max().item() + 2e-3, (name, causal)
+
+
+def test_backward_outputs_complete_for_the_next_kernel_on_the_stream(fa, dev):
+    """The dQ kernel is launched as a programmatic dependent of the dK/dV kernel; work enqueued after
+    fa_backward on the same stream - directly, and as the next node of a captured graph - must still
+    see dK and dV complete.  A copy kernel right behind fa_backward (no synchronisation in between)
+    has to read exactly what a synchronised run leaves in the buffers."""
+    bh, s, d = 48, 2048, 64
+    g = torch.Generator().manual_seed(4242)
+    q, k, v, d_o = (torch.randn((bh, s, d), generator=g).half().to(dev) for _ in range(4))
+    o = torch.empty_like(q)
+    lse = torch.empty((bh, s), device=dev, dtype=torch.float32)
+    fa.prefill(q, k, v, o, lse, 1, bh, s, d, 0.125, True)
+    wsb = fa.backward_workspace_bytes(1, bh, s)
+    ws = torch.empty(wsb, device=dev, dtype=torch.uint8)
+    gq, gk, gv = (torch.empty_like(q) for _ in range(3))
+    snap_k, snap_v = torch.empty_like(q), torch.empty_like(q)
+
+    def enqueue(stream):
+        fa.backward(q, k, v, o, d_o, lse, gq, gk, gv, 1, bh, s, d, 0.125, True, workspace=ws,
+                    workspace_bytes=wsb, stream=stream)
+        snap_k.copy_(gk)                                  # same stream, no synchronisation in between
+        snap_v.copy_(gv)
+
+    # reference: a synchronised run
+    fa.backward(q, k, v, o, d_o, lse, gq, gk, gv, 1, bh, s, d, 0.125, True, workspace=ws, workspace_bytes=wsb)
+    torch.cuda.synchronize()
+    ref_k, ref_v = gk.clone(), gv.clone()
+    assert torch.isfinite(ref_k).all() and torch.isfinite(ref_v).all()
+
+    stream = torch.cuda.Stream()
+    for _ in range(3):
+        for t in (gk, gv, snap_k, snap_v):
+            t.fill_(float("nan"))
+        torch.cuda.synchronize()
+        with torch.cuda.stream(stream):
+            enqueue(stream)
+        stream.synchronize()
+        assert torch.equal(snap_k, ref_k) and torch.equal(snap_v, ref_v)
+
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(stream):
+        with torch.cuda.graph(graph, stream=stream):
+            enqueue(stream)
+    for _ in range(3):
+        for t in (gk, gv, snap_k, snap_v):
+            t.fill_(float("nan"))
+        torch.cuda.synchronize()
+        graph.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(snap_k, ref_k) and torch.equal(snap_v, ref_v)
+    assert fa.device_status() == 0

@@ -12,7 +12,7 @@ import pytest
 
 from helpers import nrmse_and_bad, run_prefill
 
-pytestmark = pytest.mark.gpu
+pytestmark = [pytest.mark.gpu, pytest.mark.usefixtures("prefill_variant")]
 
 TOL_O_F16 = 2e-3
 TOL_LSE = 1e-3
@@ -132,12 +132,16 @@ def test_lse_optional_and_rows_beyond_s_untouched(fa, dev, oracle):
     assert np.abs(buf[:bh * s * d].float().cpu().numpy().reshape(bh, s, d) - o_ref).max() < TOL_O_F16
 
 
-def test_headline_shape_properties(fa, dev, oracle):
+def test_headline_shape_properties(fa, dev, oracle, prefill_variant):
     """B=8,H=12,S=2048,D=64 causal at full size: spot-check heads against the
     oracle, and check properties that hold at any size: row 0 attends only to
     key 0 (O[0] == V[0], LSE[0] == scale*q0.k0), and heads are independent
     (a head's result does not depend on which batch it is computed in)."""
     import torch
+    if prefill_variant == "auto":
+        # bit-identity across batch sizes holds per kernel; the library's own choice differs
+        # between 96 heads and one head, so pin the kernel the 96 heads get
+        fa.set_prefill_variant("tile_pair")
     bh, s, d = 96, 2048, 64
     q, k, v = (oracle.round_to(x, "f16") for x in oracle.normal_inputs(2002, (bh, s, d)))
     o, lse = run_prefill(fa, dev, q, k, v, 0.125, True)
