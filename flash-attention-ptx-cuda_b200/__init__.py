@@ -30,6 +30,7 @@ FA_ERR_WORKSPACE = -4
 FA_ERR_CUDA = -5
 FA_ERR_DEVICE_TIMEOUT = -6
 FA_ERR_NOT_SM100 = -7
+FA_ERR_NCCL = -8
 FA_DTYPE_F16, FA_DTYPE_BF16, FA_DTYPE_E4M3 = 0, 1, 2
 DTYPES = {"f16": FA_DTYPE_F16, "bf16": FA_DTYPE_BF16, "e4m3": FA_DTYPE_E4M3}
 
@@ -40,7 +41,8 @@ EXPORTED_SYMBOLS = (
     "fa_backward_workspace_bytes", "fa_combine", "fa_kat",
     "fa_device_status",
     "fa_clear_device_status", "fa_error_string", "fa_last_cuda_error", "fa_version",
-    "fa_set_prefill_variant",
+    "fa_set_prefill_variant", "fa_combine_packed", "fa_decode_kv_sharded", "fa_decode_kv_sharded_gather_bytes",
+    "fa_nccl_unique_id", "fa_nccl_comm_create", "fa_nccl_comm_destroy", "fa_status_word_to_error",
 )
 
 
@@ -153,6 +155,22 @@ def lib() -> ctypes.CDLL:
         l.fa_error_string.argtypes = [ctypes.c_int]
         l.fa_last_cuda_error.restype = ctypes.c_char_p
         l.fa_version.restype = ctypes.c_int
+        l.fa_combine_packed.restype = ctypes.c_int
+        l.fa_combine_packed.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_void_p,
+                                        ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p]
+        l.fa_decode_kv_sharded.restype = ctypes.c_int
+        l.fa_decode_kv_sharded.argtypes = [ctypes.POINTER(DecodeArgs), ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t]
+        l.fa_decode_kv_sharded_gather_bytes.restype = ctypes.c_size_t
+        l.fa_decode_kv_sharded_gather_bytes.argtypes = [ctypes.c_int] * 4
+        l.fa_nccl_unique_id.restype = ctypes.c_int
+        l.fa_nccl_unique_id.argtypes = [ctypes.c_void_p, ctypes.c_size_t]
+        l.fa_nccl_comm_create.restype = ctypes.c_int
+        l.fa_nccl_comm_create.argtypes = [ctypes.POINTER(ctypes.c_void_p), ctypes.c_int, ctypes.c_void_p, ctypes.c_size_t,
+                                          ctypes.c_int]
+        l.fa_nccl_comm_destroy.restype = ctypes.c_int
+        l.fa_nccl_comm_destroy.argtypes = [ctypes.c_void_p]
+        l.fa_status_word_to_error.restype = ctypes.c_int
+        l.fa_status_word_to_error.argtypes = [ctypes.c_int]
         l.fa_set_prefill_variant.restype = ctypes.c_int
         l.fa_set_prefill_variant.argtypes = [ctypes.c_int]
         _lib = l
@@ -298,6 +316,56 @@ def combine(o_parts, lse_parts, n_parts, rows, d_head, o, lse, dtype="f16", stre
                           DTYPES[dtype] if isinstance(dtype, str) else dtype, _stream_handle(stream))
     if rc != FA_OK:
         raise FaError(rc, "fa_combine")
+
+
+def combine_packed(packed_parts, n_parts, rows, d_head, o, lse, dtype="f16", stream=None) -> None:
+    """fa_combine_packed: LSE merge of [n_parts, rows, d_head + 1] fp32 partials (O then LSE per row)."""
+    rc = lib().fa_combine_packed(_ptr(packed_parts), n_parts, rows, d_head, _ptr(o), _ptr(lse),
+                                 DTYPES[dtype] if isinstance(dtype, str) else dtype, _stream_handle(stream))
+    if rc != FA_OK:
+        raise FaError(rc, "fa_combine_packed")
+
+
+NCCL_UNIQUE_ID_BYTES = 128
+
+
+def nccl_unique_id() -> bytes:
+    """fa_nccl_unique_id: a fresh NCCL id (rank 0 creates it, every rank passes it to nccl_comm_create)."""
+    buf = ctypes.create_string_buffer(NCCL_UNIQUE_ID_BYTES)
+    rc = lib().fa_nccl_unique_id(buf, NCCL_UNIQUE_ID_BYTES)
+    if rc != FA_OK:
+        raise FaError(rc, "fa_nccl_unique_id")
+    return buf.raw
+
+
+def nccl_comm_create(n_ranks: int, unique_id: bytes, rank: int) -> int:
+    """fa_nccl_comm_create: an ncclComm_t (as an integer handle) for the current device."""
+    comm = ctypes.c_void_p()
+    buf = ctypes.create_string_buffer(unique_id, NCCL_UNIQUE_ID_BYTES)
+    rc = lib().fa_nccl_comm_create(ctypes.byref(comm), n_ranks, buf, NCCL_UNIQUE_ID_BYTES, rank)
+    if rc != FA_OK:
+        raise FaError(rc, "fa_nccl_comm_create")
+    return comm.value
+
+
+def nccl_comm_destroy(comm: int) -> None:
+    rc = lib().fa_nccl_comm_destroy(comm)
+    if rc != FA_OK:
+        raise FaError(rc, "fa_nccl_comm_destroy")
+
+
+def decode_kv_sharded_gather_bytes(batch_size, num_heads, d_head, n_ranks) -> int:
+    return lib().fa_decode_kv_sharded_gather_bytes(batch_size, num_heads, d_head, n_ranks)
+
+
+def decode_kv_sharded_raw(q, k, v, o, lse, batch_size, num_heads, local_kv, d_head, scale, comm, gather,
+                          gather_bytes, dtype="f16", num_splits=0, workspace=None, workspace_bytes=0,
+                          stream=None) -> int:
+    """fa_decode_kv_sharded on this rank's key slice; returns the status code."""
+    a = DecodeArgs(_ptr(q), _ptr(k), _ptr(v), _ptr(o), _ptr(lse), None, batch_size, num_heads, local_kv,
+                   d_head, scale, DTYPES[dtype] if isinstance(dtype, str) else dtype, num_splits,
+                   _ptr(workspace), workspace_bytes, _stream_handle(stream))
+    return lib().fa_decode_kv_sharded(ctypes.byref(a), comm, _ptr(gather), gather_bytes)
 
 
 def kat(dtype: str, d_head: int, q, k, v, p_scale: float):

@@ -9,6 +9,7 @@
 #include <mutex>
 
 #include "../../include/flash_attention.h"
+#include "bounded_wait.h"
 #include "host_common.h"
 
 namespace fa {
@@ -29,6 +30,10 @@ EncodeTiledFn g_encode = nullptr;
 int note_cuda_error(cudaError_t err, const char* where) {
     snprintf(g_last_cuda_error, sizeof(g_last_cuda_error), "%s: %s", where, cudaGetErrorString(err));
     return FA_ERR_CUDA;
+}
+int note_message(const char* msg, int code) {
+    snprintf(g_last_cuda_error, sizeof(g_last_cuda_error), "%s", msg);
+    return code;
 }
 int note_driver_error(CUresult err, const char* where) {
     snprintf(g_last_cuda_error, sizeof(g_last_cuda_error), "%s: CUresult %d", where, (int)err);
@@ -241,7 +246,7 @@ FA_EXPORT int fa_prefill_host(const fa_prefill_args* h) {
     for (int i = 0; i < 3; i++) FA_CUDA_TRY(cudaStreamSynchronize(st->pipe[i]));
     int word = 0;
     FA_CUDA_TRY(cudaMemcpy(&word, st->status, sizeof(int), cudaMemcpyDeviceToHost));
-    return word == 0 ? FA_OK : FA_ERR_DEVICE_TIMEOUT;
+    return status_word_to_error(word);
 }
 
 FA_EXPORT int fa_device_status(int* status_word) {
@@ -251,8 +256,10 @@ FA_EXPORT int fa_device_status(int* status_word) {
     int word = 0;
     FA_CUDA_TRY(cudaMemcpy(&word, st->status, sizeof(int), cudaMemcpyDeviceToHost));
     if (status_word) *status_word = word;
-    return word == 0 ? FA_OK : FA_ERR_DEVICE_TIMEOUT;
+    return status_word_to_error(word);
 }
+
+FA_EXPORT int fa_status_word_to_error(int status_word) { return status_word_to_error(status_word); }
 
 FA_EXPORT int fa_clear_device_status(void) {
     DeviceState* st = device_state();
@@ -272,6 +279,7 @@ FA_EXPORT const char* fa_error_string(int code) {
         case FA_ERR_CUDA:             return "CUDA call failed";
         case FA_ERR_DEVICE_TIMEOUT:   return "a kernel gave up on a bounded wait";
         case FA_ERR_NOT_SM100:        return "device is not compute capability 10.x";
+        case FA_ERR_NCCL:             return "NCCL call failed or libnccl not found";
         default:                      return "unknown error";
     }
 }

@@ -6,7 +6,7 @@
 // one query row the work is one multiply-add per byte of K and V read, so the
 // kernels here are built around HBM traffic, not tensor cores:
 //
-//   decode_partial_kernel  grid (splits, batch*heads).  Each warp streams rows
+//   decode_partial_kernel  grid batch*heads x splits (one-dimensional).  Each warp streams rows
 //     of K and V straight from global memory with 128-bit loads (a 16-lane group
 //     covers one 256-byte row at d_head 128, so every warp instruction reads
 //     whole rows, fully coalesced), keeps an online softmax (running max, sum,
@@ -23,6 +23,12 @@
 #include <cmath>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
+#include <dlfcn.h>
+#include <nccl.h>
+
+#include <atomic>
+#include <cstdio>
+#include <cstring>
 #include <mutex>
 
 #include "host_common.h"
@@ -84,7 +90,8 @@ decode_partial_kernel(const uint16_t* __restrict__ q, const uint16_t* __restrict
     constexpr int LPR = D / 8;           // lanes covering one row (8 elements = 16 bytes per lane)
     constexpr int RPW = 32 / LPR;        // rows per warp-wide load
     constexpr int STEP = kDecodeWarps * RPW;
-    const int split = blockIdx.x, bh = blockIdx.y;
+    // one-dimensional grid: the splits of a head are neighbours, and batch * heads is not limited to 65535
+    const int bh = blockIdx.x / n_splits, split = blockIdx.x - bh * n_splits;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int sub = lane / LPR;          // which row of the warp-wide load this lane reads
     const int dsl = (lane % LPR) * 8;    // first of this lane's 8 head-dim elements
@@ -186,13 +193,16 @@ decode_partial_kernel(const uint16_t* __restrict__ q, const uint16_t* __restrict
     }
 }
 
-// One CTA per output row, one thread per head-dim element.
+// One CTA per output row, one thread per head-dim element.  Inputs and the fp32 output are
+// addressed by strides, so the same kernel reads split partials ([row][split][D]), gathered
+// per-rank partials ([rank][row][D]) and packed ones ([rank][row][D + 1], LSE in the last
+// column), and can write a packed row itself.
 template <bool BF16>
 __global__ void combine_kernel(const float* __restrict__ o_parts, const float* __restrict__ lse_parts,
                                int n_parts, long long part_stride_o, long long row_stride_o,
                                long long part_stride_l, long long row_stride_l, int d_head,
-                               uint16_t* __restrict__ o, float* __restrict__ lse,
-                               float* __restrict__ o_f32) {
+                               uint16_t* __restrict__ o, float* __restrict__ lse, long long lse_stride,
+                               float* __restrict__ o_f32, long long o_f32_stride) {
     const int row = blockIdx.x, d = threadIdx.x;
     const float* lp = lse_parts + (size_t)row * row_stride_l;
     float m = -INFINITY;
@@ -213,24 +223,114 @@ __global__ void combine_kernel(const float* __restrict__ o_parts, const float* _
         else bits = __half_as_ushort(__float2half_rn(out));
         o[(size_t)row * d_head + d] = bits;
     }
-    if (o_f32 != nullptr) o_f32[(size_t)row * d_head + d] = out;
-    if (lse != nullptr && d == 0) lse[row] = wsum > 0.0f ? m + kLn2 * log2f(wsum) : -INFINITY;
+    if (o_f32 != nullptr) o_f32[(size_t)row * o_f32_stride + d] = out;
+    if (lse != nullptr && d == 0) lse[(size_t)row * lse_stride] = wsum > 0.0f ? m + kLn2 * log2f(wsum) : -INFINITY;
 }
 
+// A rank that holds no key of a KV-sequence-sharded cache contributes weight zero to the merge.
+__global__ void empty_partial_kernel(float* packed, int d_head) {
+    float* row = packed + (size_t)blockIdx.x * (d_head + 1);
+    row[threadIdx.x] = 0.0f;
+    if (threadIdx.x == 0) row[d_head] = -INFINITY;
+}
+
+struct CombineOut {
+    void*     o = nullptr;           // 16-bit [rows][D], optional
+    float*    lse = nullptr;         // optional
+    long long lse_stride = 1;
+    float*    o_f32 = nullptr;       // optional
+    long long o_f32_stride = 0;
+};
+
 int launch_combine(const float* o_parts, const float* lse_parts, int n_parts, long long pso,
-                   long long rso, long long psl, long long rsl, int rows, int d_head, void* o,
-                   float* lse, float* o_f32, int dtype, cudaStream_t stream) {
+                   long long rso, long long psl, long long rsl, int rows, int d_head, const CombineOut& out,
+                   int dtype, cudaStream_t stream) {
     if (dtype == FA_DTYPE_BF16)
-        combine_kernel<true><<<rows, d_head, 0, stream>>>(o_parts, lse_parts, n_parts, pso, rso, psl, rsl,
-                                                          d_head, static_cast<uint16_t*>(o), lse, o_f32);
+        combine_kernel<true><<<rows, d_head, 0, stream>>>(o_parts, lse_parts, n_parts, pso, rso, psl, rsl, d_head,
+                                                          static_cast<uint16_t*>(out.o), out.lse, out.lse_stride,
+                                                          out.o_f32, out.o_f32_stride);
     else
-        combine_kernel<false><<<rows, d_head, 0, stream>>>(o_parts, lse_parts, n_parts, pso, rso, psl, rsl,
-                                                           d_head, static_cast<uint16_t*>(o), lse, o_f32);
+        combine_kernel<false><<<rows, d_head, 0, stream>>>(o_parts, lse_parts, n_parts, pso, rso, psl, rsl, d_head,
+                                                           static_cast<uint16_t*>(out.o), out.lse, out.lse_stride,
+                                                           out.o_f32, out.o_f32_stride);
     FA_CUDA_TRY(cudaGetLastError());
     return FA_OK;
 }
 
 size_t align256(size_t x) { return (x + 255) & ~size_t(255); }
+
+int default_splits(int sms, long long bh, int seq_len_kv) {
+    // Enough CTAs for ~8 per SM, but never fewer than 512 keys per split.
+    long long want = (8ll * sms + bh - 1) / bh;
+    long long max_by_len = seq_len_kv / 512 > 0 ? seq_len_kv / 512 : 1;
+    long long s = want < max_by_len ? want : max_by_len;
+    if (s < 1) s = 1;
+    if (s > FA_MAX_SPLITS) s = FA_MAX_SPLITS;
+    return (int)s;
+}
+
+// Argument checks shared by every entry point that takes fa_decode_args.
+int validate_decode(const fa_decode_args* a, bool need_output) {
+    if (!a || !a->q || !a->k || !a->v) return FA_ERR_INVALID_ARGUMENT;
+    if (need_output) {
+        if (!a->o && !a->o_f32) return FA_ERR_INVALID_ARGUMENT;
+        if (a->o_f32 && !a->lse) return FA_ERR_INVALID_ARGUMENT;
+    }
+    if (a->batch_size <= 0 || a->num_heads <= 0 || a->seq_len_kv <= 0) return FA_ERR_INVALID_ARGUMENT;
+    if (!(a->scale > 0.0f) || !std::isfinite(a->scale)) return FA_ERR_INVALID_ARGUMENT;
+    if (a->dtype != FA_DTYPE_F16 && a->dtype != FA_DTYPE_BF16) return FA_ERR_UNSUPPORTED;
+    if (a->d_head != 64 && a->d_head != 128) return FA_ERR_UNSUPPORTED;
+    if (a->num_splits < 0 || a->num_splits > FA_MAX_SPLITS) return FA_ERR_UNSUPPORTED;
+    const long long bh = (long long)a->batch_size * a->num_heads;
+    if (bh * FA_MAX_SPLITS > 0x7FFFFFFFll) return FA_ERR_UNSUPPORTED;   // grid.x
+    if (!aligned16(a->q) || !aligned16(a->k) || !aligned16(a->v) || (a->o && !aligned16(a->o)))
+        return FA_ERR_MISALIGNED;
+    return FA_OK;
+}
+
+// The split count actually used: the caller's or the default, with no empty trailing split.
+void plan_splits(const fa_decode_args* a, int sm_count, int* splits_out, int* keys_per_split_out) {
+    const long long bh = (long long)a->batch_size * a->num_heads;
+    int splits = a->num_splits ? a->num_splits : default_splits(sm_count, bh, a->seq_len_kv);
+    if (splits > a->seq_len_kv) splits = a->seq_len_kv;
+    const int kps = (a->seq_len_kv + splits - 1) / splits;
+    *splits_out = (a->seq_len_kv + kps - 1) / kps;
+    *keys_per_split_out = kps;
+}
+
+// The two launches of a decode step: per-split partials into `scratch` (fp32 O [bh][split][D], then,
+// 256-byte aligned, LSE [bh][split]), and their merge into `out`.  Shared by fa_decode (caller's
+// workspace), fa_decode_static (the built-in array) and the KV-sharded entry (packed output).
+int decode_into(const fa_decode_args* a, int splits, int kps, void* scratch, const CombineOut& out) {
+    const long long bh = (long long)a->batch_size * a->num_heads;
+    float* o_part = static_cast<float*>(scratch);
+    float* lse_part = reinterpret_cast<float*>(static_cast<uint8_t*>(scratch) +
+                                               align256((size_t)bh * splits * a->d_head * sizeof(float)));
+    cudaStream_t stream = static_cast<cudaStream_t>(a->stream);
+    const unsigned grid = (unsigned)(bh * splits);
+    const float sl2 = a->scale * kLog2e;
+    const uint16_t* q = static_cast<const uint16_t*>(a->q);
+    const uint16_t* k = static_cast<const uint16_t*>(a->k);
+    const uint16_t* v = static_cast<const uint16_t*>(a->v);
+    const bool bf = a->dtype == FA_DTYPE_BF16;
+#define FA_LAUNCH_DECODE(DH, BF) \
+    decode_partial_kernel<DH, BF><<<grid, kDecodeWarps * 32, 0, stream>>>(q, k, v, o_part, lse_part, \
+        a->seq_len_kv, splits, kps, sl2)
+    if (a->d_head == 128) { if (bf) FA_LAUNCH_DECODE(128, true); else FA_LAUNCH_DECODE(128, false); }
+    else                  { if (bf) FA_LAUNCH_DECODE(64, true);  else FA_LAUNCH_DECODE(64, false); }
+#undef FA_LAUNCH_DECODE
+    FA_CUDA_TRY(cudaGetLastError());
+    // partials: o [bh][split][D], lse [bh][split]
+    return launch_combine(o_part, lse_part, splits, a->d_head, (long long)splits * a->d_head, 1, splits,
+                          (int)bh, a->d_head, out, a->dtype, stream);
+}
+
+CombineOut caller_outputs(const fa_decode_args* a) {
+    CombineOut out;
+    out.o = a->o; out.lse = a->lse; out.lse_stride = 1;
+    out.o_f32 = a->o_f32; out.o_f32_stride = a->d_head;
+    return out;
+}
 
 }  // namespace
 }  // namespace fa
@@ -246,62 +346,20 @@ FA_EXPORT size_t fa_decode_workspace_bytes(int batch_size, int num_heads, int d_
 FA_EXPORT int fa_decode_default_splits(int batch_size, int num_heads, int seq_len_kv) {
     if (batch_size <= 0 || num_heads <= 0 || seq_len_kv <= 0) return 0;
     DeviceState* st = device_state();
-    const int sms = st ? st->sm_count : 148;
-    const long long bh = (long long)batch_size * num_heads;
-    // Enough CTAs for ~8 per SM, but never fewer than 512 keys per split.
-    long long want = (8ll * sms + bh - 1) / bh;
-    long long max_by_len = seq_len_kv / 512 > 0 ? seq_len_kv / 512 : 1;
-    long long s = want < max_by_len ? want : max_by_len;
-    if (s < 1) s = 1;
-    if (s > FA_MAX_SPLITS) s = FA_MAX_SPLITS;
-    return (int)s;
+    return default_splits(st ? st->sm_count : 148, (long long)batch_size * num_heads, seq_len_kv);
 }
 
 FA_EXPORT int fa_decode(const fa_decode_args* a) {
-    if (!a || !a->q || !a->k || !a->v) return FA_ERR_INVALID_ARGUMENT;
-    if (!a->o && !a->o_f32) return FA_ERR_INVALID_ARGUMENT;
-    if (a->o_f32 && !a->lse) return FA_ERR_INVALID_ARGUMENT;
-    if (a->batch_size <= 0 || a->num_heads <= 0 || a->seq_len_kv <= 0) return FA_ERR_INVALID_ARGUMENT;
-    if (!(a->scale > 0.0f) || !std::isfinite(a->scale)) return FA_ERR_INVALID_ARGUMENT;
-    if (a->dtype != FA_DTYPE_F16 && a->dtype != FA_DTYPE_BF16) return FA_ERR_UNSUPPORTED;
-    if (a->d_head != 64 && a->d_head != 128) return FA_ERR_UNSUPPORTED;
-    if (a->num_splits < 0 || a->num_splits > FA_MAX_SPLITS) return FA_ERR_UNSUPPORTED;
-    const long long bh = (long long)a->batch_size * a->num_heads;
-    if (bh > 65535) return FA_ERR_UNSUPPORTED;      // grid.y
-    if (!aligned16(a->q) || !aligned16(a->k) || !aligned16(a->v) || (a->o && !aligned16(a->o)))
-        return FA_ERR_MISALIGNED;
+    int rc = validate_decode(a, true);
+    if (rc != FA_OK) return rc;
     DeviceState* st = device_state();
     if (!st) return FA_ERR_CUDA;
     if (st->cc_major != 10) return FA_ERR_NOT_SM100;
-
-    int splits = a->num_splits ? a->num_splits
-                               : fa_decode_default_splits(a->batch_size, a->num_heads, a->seq_len_kv);
-    if (splits > a->seq_len_kv) splits = a->seq_len_kv;
-    int kps = (a->seq_len_kv + splits - 1) / splits;
-    splits = (a->seq_len_kv + kps - 1) / kps;        // no empty trailing split
+    int splits, kps;
+    plan_splits(a, st->sm_count, &splits, &kps);
     const size_t need = fa_decode_workspace_bytes(a->batch_size, a->num_heads, a->d_head, splits);
     if (!a->workspace || a->workspace_bytes < need || !aligned16(a->workspace)) return FA_ERR_WORKSPACE;
-
-    float* o_part = static_cast<float*>(a->workspace);
-    float* lse_part = reinterpret_cast<float*>(static_cast<uint8_t*>(a->workspace) +
-                                               align256((size_t)bh * splits * a->d_head * sizeof(float)));
-    cudaStream_t stream = static_cast<cudaStream_t>(a->stream);
-    const dim3 grid(splits, (unsigned)bh);
-    const float sl2 = a->scale * kLog2e;
-    const uint16_t* q = static_cast<const uint16_t*>(a->q);
-    const uint16_t* k = static_cast<const uint16_t*>(a->k);
-    const uint16_t* v = static_cast<const uint16_t*>(a->v);
-    const bool bf = a->dtype == FA_DTYPE_BF16;
-#define FA_LAUNCH_DECODE(DH, BF) \
-    decode_partial_kernel<DH, BF><<<grid, kDecodeWarps * 32, 0, stream>>>(q, k, v, o_part, lse_part, \
-        a->seq_len_kv, splits, kps, sl2)
-    if (a->d_head == 128) { if (bf) FA_LAUNCH_DECODE(128, true); else FA_LAUNCH_DECODE(128, false); }
-    else                  { if (bf) FA_LAUNCH_DECODE(64, true);  else FA_LAUNCH_DECODE(64, false); }
-#undef FA_LAUNCH_DECODE
-    FA_CUDA_TRY(cudaGetLastError());
-    // partials: o [bh][split][D], lse [bh][split]
-    return launch_combine(o_part, lse_part, splits, a->d_head, (long long)splits * a->d_head, 1, splits,
-                          (int)bh, a->d_head, a->o, a->lse, a->o_f32, a->dtype, stream);
+    return decode_into(a, splits, kps, a->workspace, caller_outputs(a));
 }
 
 // ---------------------------------------------------------------------------
@@ -321,29 +379,35 @@ namespace {
 static __device__ __align__(256) unsigned char g_decode_static_scratch[FA_DECODE_STATIC_SCRATCH_BYTES];
 
 struct StaticScratchSetup {
-    bool  ready = false;
-    void* ptr = nullptr;      // device address of g_decode_static_scratch on this device
+    std::atomic<bool> ready{false};   // release-stored after the fields below, acquire-loaded before them
+    void* ptr = nullptr;              // device address of g_decode_static_scratch on this device
     int   cc_major = 0;
     int   sm_count = 0;
 };
 StaticScratchSetup g_static_setup[64];
 std::mutex g_static_mutex;
 
-// First call on a device: resolve the array's device address.  Returns FA_OK or an error code.
+// First call on a device: check the device, then resolve the array's device address.
 int static_scratch_setup(StaticScratchSetup** out) {
     int dev = 0;
     FA_CUDA_TRY(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64) return FA_ERR_INVALID_ARGUMENT;
     StaticScratchSetup* s = &g_static_setup[dev];
-    if (!s->ready) {
+    if (!s->ready.load(std::memory_order_acquire)) {
         std::lock_guard<std::mutex> lock(g_static_mutex);
-        if (!s->ready) {
+        if (!s->ready.load(std::memory_order_relaxed)) {
+            int major = 0, sms = 0;
+            FA_CUDA_TRY(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev));
+            FA_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+            // before the symbol lookup: on another architecture the library holds no image for the
+            // device and the lookup would fail with a less helpful error
+            if (major != 10) return FA_ERR_NOT_SM100;
             void* ptr = nullptr;
             FA_CUDA_TRY(cudaGetSymbolAddress(&ptr, g_decode_static_scratch));
-            FA_CUDA_TRY(cudaDeviceGetAttribute(&s->cc_major, cudaDevAttrComputeCapabilityMajor, dev));
-            FA_CUDA_TRY(cudaDeviceGetAttribute(&s->sm_count, cudaDevAttrMultiProcessorCount, dev));
             s->ptr = ptr;
-            s->ready = true;
+            s->cc_major = major;
+            s->sm_count = sms;
+            s->ready.store(true, std::memory_order_release);
         }
     }
     *out = s;
@@ -354,55 +418,17 @@ int static_scratch_setup(StaticScratchSetup** out) {
 }  // namespace fa
 
 FA_EXPORT int fa_decode_static(const fa_decode_args* a) {
-    if (!a || !a->q || !a->k || !a->v) return FA_ERR_INVALID_ARGUMENT;
-    if (!a->o && !a->o_f32) return FA_ERR_INVALID_ARGUMENT;
-    if (a->o_f32 && !a->lse) return FA_ERR_INVALID_ARGUMENT;
-    if (a->batch_size <= 0 || a->num_heads <= 0 || a->seq_len_kv <= 0) return FA_ERR_INVALID_ARGUMENT;
-    if (!(a->scale > 0.0f) || !std::isfinite(a->scale)) return FA_ERR_INVALID_ARGUMENT;
-    if (a->dtype != FA_DTYPE_F16 && a->dtype != FA_DTYPE_BF16) return FA_ERR_UNSUPPORTED;
-    if (a->d_head != 64 && a->d_head != 128) return FA_ERR_UNSUPPORTED;
-    if (a->num_splits < 0 || a->num_splits > FA_MAX_SPLITS) return FA_ERR_UNSUPPORTED;
-    const long long bh = (long long)a->batch_size * a->num_heads;
-    if (bh > 65535) return FA_ERR_UNSUPPORTED;
-    if (!aligned16(a->q) || !aligned16(a->k) || !aligned16(a->v) || (a->o && !aligned16(a->o)))
-        return FA_ERR_MISALIGNED;
-    StaticScratchSetup* su = nullptr;
-    int rc = static_scratch_setup(&su);
+    int rc = validate_decode(a, true);
     if (rc != FA_OK) return rc;
-    if (su->cc_major != 10) return FA_ERR_NOT_SM100;
-
-    int splits = a->num_splits;
-    if (splits == 0) {          // same rule as fa_decode_default_splits, from the cached SM count
-        long long want = (8ll * su->sm_count + bh - 1) / bh;
-        long long max_by_len = a->seq_len_kv / 512 > 0 ? a->seq_len_kv / 512 : 1;
-        long long s = want < max_by_len ? want : max_by_len;
-        splits = (int)(s < 1 ? 1 : (s > FA_MAX_SPLITS ? FA_MAX_SPLITS : s));
-    }
-    if (splits > a->seq_len_kv) splits = a->seq_len_kv;
-    const int kps = (a->seq_len_kv + splits - 1) / splits;
-    splits = (a->seq_len_kv + kps - 1) / kps;
-    const size_t o_bytes = align256((size_t)bh * splits * a->d_head * sizeof(float));
-    const size_t l_bytes = align256((size_t)bh * splits * sizeof(float));
-    if (o_bytes + l_bytes > (size_t)FA_DECODE_STATIC_SCRATCH_BYTES) return FA_ERR_WORKSPACE;
-
-    float* o_part = static_cast<float*>(su->ptr);
-    float* lse_part = reinterpret_cast<float*>(static_cast<unsigned char*>(su->ptr) + o_bytes);
-    cudaStream_t stream = static_cast<cudaStream_t>(a->stream);
-    const dim3 grid(splits, (unsigned)bh);
-    const float sl2 = a->scale * kLog2e;
-    const uint16_t* q = static_cast<const uint16_t*>(a->q);
-    const uint16_t* k = static_cast<const uint16_t*>(a->k);
-    const uint16_t* v = static_cast<const uint16_t*>(a->v);
-    const bool bf = a->dtype == FA_DTYPE_BF16;
-#define FA_LAUNCH_DECODE_STATIC(DH, BF) \
-    decode_partial_kernel<DH, BF><<<grid, kDecodeWarps * 32, 0, stream>>>(q, k, v, o_part, lse_part, \
-        a->seq_len_kv, splits, kps, sl2)
-    if (a->d_head == 128) { if (bf) FA_LAUNCH_DECODE_STATIC(128, true); else FA_LAUNCH_DECODE_STATIC(128, false); }
-    else                  { if (bf) FA_LAUNCH_DECODE_STATIC(64, true);  else FA_LAUNCH_DECODE_STATIC(64, false); }
-#undef FA_LAUNCH_DECODE_STATIC
-    FA_CUDA_TRY(cudaGetLastError());
-    return launch_combine(o_part, lse_part, splits, a->d_head, (long long)splits * a->d_head, 1, splits,
-                          (int)bh, a->d_head, a->o, a->lse, a->o_f32, a->dtype, stream);
+    StaticScratchSetup* su = nullptr;
+    rc = static_scratch_setup(&su);
+    if (rc != FA_OK) return rc;
+    int splits, kps;
+    plan_splits(a, su->sm_count, &splits, &kps);
+    if (fa_decode_workspace_bytes(a->batch_size, a->num_heads, a->d_head, splits) >
+        (size_t)FA_DECODE_STATIC_SCRATCH_BYTES)
+        return FA_ERR_WORKSPACE;
+    return decode_into(a, splits, kps, su->ptr, caller_outputs(a));
 }
 
 // ---------------------------------------------------------------------------
@@ -515,8 +541,10 @@ FA_EXPORT int fa_decode_gqa(const fa_decode_gqa_args* a) {
     int rc = launch_decode_gqa(g, st);
     if (rc != FA_OK) return rc;
     if (splits == 1) return FA_OK;                      // the kernel wrote o and lse itself
+    CombineOut out;
+    out.o = a->o; out.lse = a->lse;
     return launch_combine(o_part, lse_part, splits, a->d_head, (long long)splits * a->d_head, 1, splits,
-                          (int)rows, a->d_head, a->o, a->lse, nullptr, e4m3 ? FA_DTYPE_BF16 : a->dtype, stream);
+                          (int)rows, a->d_head, out, e4m3 ? FA_DTYPE_BF16 : a->dtype, stream);
 }
 
 FA_EXPORT int fa_combine(const float* o_parts, const float* lse_parts, int n_parts, int rows,
@@ -527,6 +555,158 @@ FA_EXPORT int fa_combine(const float* o_parts, const float* lse_parts, int n_par
     DeviceState* st = device_state();
     if (!st) return FA_ERR_CUDA;
     // gathered layout: o [part][row][D], lse [part][row]
+    CombineOut out;
+    out.o = o; out.lse = lse;
     return launch_combine(o_parts, lse_parts, n_parts, (long long)rows * d_head, d_head, rows, 1, rows,
-                          d_head, o, lse, nullptr, dtype, static_cast<cudaStream_t>(stream));
+                          d_head, out, dtype, static_cast<cudaStream_t>(stream));
+}
+
+FA_EXPORT int fa_combine_packed(const float* packed_parts, int n_parts, int rows, int d_head, void* o,
+                                float* lse, int dtype, void* stream) {
+    if (!packed_parts || !o || n_parts <= 0 || rows <= 0) return FA_ERR_INVALID_ARGUMENT;
+    if (d_head != 64 && d_head != 128) return FA_ERR_UNSUPPORTED;
+    if (dtype != FA_DTYPE_F16 && dtype != FA_DTYPE_BF16) return FA_ERR_UNSUPPORTED;
+    DeviceState* st = device_state();
+    if (!st) return FA_ERR_CUDA;
+    // [part][row][D + 1]: the merge reads the all-gather's receive buffer where it lies
+    const long long w = d_head + 1;
+    CombineOut out;
+    out.o = o; out.lse = lse;
+    return launch_combine(packed_parts, packed_parts + d_head, n_parts, (long long)rows * w, w, (long long)rows * w, w,
+                          rows, d_head, out, dtype, static_cast<cudaStream_t>(stream));
+}
+
+// ---------------------------------------------------------------------------
+// KV-sequence-sharded decode: the local partial, the one all-gather and the merge
+// behind one call.  NCCL is reached through dlopen so that the library has no
+// link-time dependency on it (a process that never shards never loads it).
+// ---------------------------------------------------------------------------
+namespace fa {
+namespace {
+
+struct NcclApi {
+    void* handle = nullptr;
+    ncclResult_t (*get_unique_id)(ncclUniqueId*) = nullptr;
+    ncclResult_t (*comm_init_rank)(ncclComm_t*, int, ncclUniqueId, int) = nullptr;
+    ncclResult_t (*comm_destroy)(ncclComm_t) = nullptr;
+    ncclResult_t (*comm_count)(const ncclComm_t, int*) = nullptr;
+    ncclResult_t (*comm_user_rank)(const ncclComm_t, int*) = nullptr;
+    ncclResult_t (*all_gather)(const void*, void*, size_t, ncclDataType_t, ncclComm_t, cudaStream_t) = nullptr;
+    const char* (*get_error_string)(ncclResult_t) = nullptr;
+};
+NcclApi g_nccl;
+std::once_flag g_nccl_once;
+
+// The NCCL already in the process (torch brings its own) or the system one.
+const NcclApi* nccl_api() {
+    std::call_once(g_nccl_once, [] {
+        void* h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
+        if (!h) h = dlopen("libnccl.so", RTLD_NOW | RTLD_GLOBAL);
+        if (!h) return;
+        NcclApi api;
+        api.handle = h;
+        api.get_unique_id = reinterpret_cast<decltype(api.get_unique_id)>(dlsym(h, "ncclGetUniqueId"));
+        api.comm_init_rank = reinterpret_cast<decltype(api.comm_init_rank)>(dlsym(h, "ncclCommInitRank"));
+        api.comm_destroy = reinterpret_cast<decltype(api.comm_destroy)>(dlsym(h, "ncclCommDestroy"));
+        api.comm_count = reinterpret_cast<decltype(api.comm_count)>(dlsym(h, "ncclCommCount"));
+        api.comm_user_rank = reinterpret_cast<decltype(api.comm_user_rank)>(dlsym(h, "ncclCommUserRank"));
+        api.all_gather = reinterpret_cast<decltype(api.all_gather)>(dlsym(h, "ncclAllGather"));
+        api.get_error_string = reinterpret_cast<decltype(api.get_error_string)>(dlsym(h, "ncclGetErrorString"));
+        if (api.get_unique_id && api.comm_init_rank && api.comm_destroy && api.comm_count && api.comm_user_rank &&
+            api.all_gather)
+            g_nccl = api;
+    });
+    return g_nccl.handle ? &g_nccl : nullptr;
+}
+
+int note_nccl_error(const NcclApi* api, ncclResult_t r, const char* where) {
+    char msg[200];
+    snprintf(msg, sizeof(msg), "%s: NCCL %s", where,
+             api && api->get_error_string ? api->get_error_string(r) : "error");
+    return note_message(msg, FA_ERR_NCCL);
+}
+
+}  // namespace
+}  // namespace fa
+
+FA_EXPORT int fa_nccl_unique_id(void* id_out, size_t id_bytes) {
+    if (!id_out || id_bytes < sizeof(ncclUniqueId)) return FA_ERR_INVALID_ARGUMENT;
+    const NcclApi* api = nccl_api();
+    if (!api) return note_message("libnccl.so.2 not found", FA_ERR_NCCL);
+    ncclUniqueId id;
+    ncclResult_t r = api->get_unique_id(&id);
+    if (r != ncclSuccess) return note_nccl_error(api, r, "ncclGetUniqueId");
+    memcpy(id_out, &id, sizeof(id));
+    return FA_OK;
+}
+
+FA_EXPORT int fa_nccl_comm_create(void** comm_out, int n_ranks, const void* id, size_t id_bytes, int rank) {
+    if (!comm_out || !id || id_bytes < sizeof(ncclUniqueId) || n_ranks <= 0 || rank < 0 || rank >= n_ranks)
+        return FA_ERR_INVALID_ARGUMENT;
+    const NcclApi* api = nccl_api();
+    if (!api) return note_message("libnccl.so.2 not found", FA_ERR_NCCL);
+    ncclUniqueId uid;
+    memcpy(&uid, id, sizeof(uid));
+    ncclComm_t comm = nullptr;
+    ncclResult_t r = api->comm_init_rank(&comm, n_ranks, uid, rank);
+    if (r != ncclSuccess) return note_nccl_error(api, r, "ncclCommInitRank");
+    *comm_out = comm;
+    return FA_OK;
+}
+
+FA_EXPORT int fa_nccl_comm_destroy(void* comm) {
+    if (!comm) return FA_OK;
+    const NcclApi* api = nccl_api();
+    if (!api) return note_message("libnccl.so.2 not found", FA_ERR_NCCL);
+    ncclResult_t r = api->comm_destroy(static_cast<ncclComm_t>(comm));
+    return r == ncclSuccess ? FA_OK : note_nccl_error(api, r, "ncclCommDestroy");
+}
+
+FA_EXPORT size_t fa_decode_kv_sharded_gather_bytes(int batch_size, int num_heads, int d_head, int n_ranks) {
+    if (batch_size <= 0 || num_heads <= 0 || d_head <= 0 || n_ranks <= 0) return 0;
+    return (size_t)n_ranks * batch_size * num_heads * (d_head + 1) * sizeof(float);
+}
+
+FA_EXPORT int fa_decode_kv_sharded(const fa_decode_args* a, void* nccl_comm, float* gather, size_t gather_bytes) {
+    if (!a || !nccl_comm || !gather || !a->o) return FA_ERR_INVALID_ARGUMENT;
+    const bool no_keys = a->seq_len_kv == 0;              // this rank's slice of the cache is empty
+    fa_decode_args local = *a;
+    if (no_keys) { local.seq_len_kv = 1; if (!local.k) local.k = a->q; if (!local.v) local.v = a->q; }
+    int rc = validate_decode(&local, false);
+    if (rc != FA_OK) return rc;
+    const NcclApi* api = nccl_api();
+    if (!api) return note_message("libnccl.so.2 not found", FA_ERR_NCCL);
+    DeviceState* st = device_state();
+    if (!st) return FA_ERR_CUDA;
+    if (st->cc_major != 10) return FA_ERR_NOT_SM100;
+    ncclComm_t comm = static_cast<ncclComm_t>(nccl_comm);
+    int n_ranks = 0, rank = 0;
+    ncclResult_t r = api->comm_count(comm, &n_ranks);
+    if (r == ncclSuccess) r = api->comm_user_rank(comm, &rank);
+    if (r != ncclSuccess) return note_nccl_error(api, r, "ncclCommCount");
+    const int rows = a->batch_size * a->num_heads;
+    const size_t per_rank = (size_t)rows * (a->d_head + 1);
+    if (gather_bytes < fa_decode_kv_sharded_gather_bytes(a->batch_size, a->num_heads, a->d_head, n_ranks) ||
+        !aligned16(gather))
+        return FA_ERR_WORKSPACE;
+    cudaStream_t stream = static_cast<cudaStream_t>(a->stream);
+    float* mine = gather + (size_t)rank * per_rank;       // this rank's rows of the receive buffer
+    if (no_keys) {
+        empty_partial_kernel<<<rows, a->d_head, 0, stream>>>(mine, a->d_head);
+        FA_CUDA_TRY(cudaGetLastError());
+    } else {
+        int splits, kps;
+        plan_splits(a, st->sm_count, &splits, &kps);
+        const size_t need = fa_decode_workspace_bytes(a->batch_size, a->num_heads, a->d_head, splits);
+        if (!a->workspace || a->workspace_bytes < need || !aligned16(a->workspace)) return FA_ERR_WORKSPACE;
+        // the merge of the local splits writes this rank's packed rows straight into the receive buffer
+        CombineOut out;
+        out.o_f32 = mine; out.o_f32_stride = a->d_head + 1;
+        out.lse = mine + a->d_head; out.lse_stride = a->d_head + 1;
+        if ((rc = decode_into(a, splits, kps, a->workspace, out)) != FA_OK) return rc;
+    }
+    // in place: the send buffer is this rank's block of the receive buffer
+    r = api->all_gather(mine, gather, per_rank, ncclFloat, comm, stream);
+    if (r != ncclSuccess) return note_nccl_error(api, r, "ncclAllGather");
+    return fa_combine_packed(gather, n_ranks, rows, a->d_head, a->o, a->lse, a->dtype, a->stream);
 }

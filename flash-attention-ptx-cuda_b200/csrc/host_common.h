@@ -36,6 +36,8 @@ DeviceState* device_state();
 // Remembers a CUDA failure for fa_last_cuda_error() and returns FA_ERR_CUDA.
 int note_cuda_error(cudaError_t err, const char* where);
 int note_driver_error(CUresult err, const char* where);
+// Remembers `msg` for fa_last_cuda_error() and returns `code`.
+int note_message(const char* msg, int code);
 
 #define FA_CUDA_TRY(expr)                                               \
     do {                                                                \

@@ -75,7 +75,7 @@ constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 constexpr float kRescaleThreshold = 8.0f;   // log2 units: rescale only if max grew > 2^8
 #ifndef FA_GROUP_MB
-#define FA_GROUP_MB 48
+#define FA_GROUP_MB 16
 #endif
 
 // Barrier ids reported in the status word when a wait gives up.
@@ -90,16 +90,6 @@ __device__ __forceinline__ uint32_t e4m3x2_to_f16x2(uint16_t v) {
     return r;
 }
 
-#ifdef FA_PHASE_TIMING
-// Development aid (not compiled into the shipped library): clock stamps of one CTA.
-__device__ long long g_phase_ts[3][64][8];
-__device__ long long g_cta_ts[4096][8];
-#define FA_TS(who, j, k) do { if (blockIdx.x == FA_PHASE_TIMING && (j) < 64) g_phase_ts[who][j][k] = clock64(); } while (0)
-#define FA_CTS(i, k) do { if ((i) < 4096) { g_cta_ts[i][k] = clock64(); } } while (0)
-#else
-#define FA_TS(who, j, k) do {} while (0)
-#define FA_CTS(i, k) do {} while (0)
-#endif
 
 template <int D, bool FP8>
 struct PrefillSmem {
@@ -148,7 +138,7 @@ __device__ __forceinline__ size_t gqa_partial_index(const GqaDev& gq, const Item
     return row * gq.n_splits + it.split;
 }
 
-template <bool CAUSAL, bool GQA>
+template <bool CAUSAL, bool GQA, bool GROUPED>
 __device__ __forceinline__ bool get_item(int k, int n_items, int n_bh, int n_qtiles, int seq_len,
                                          const GqaDev& gq, Item& it) {
     const int G = gridDim.x, c = blockIdx.x;
@@ -180,15 +170,22 @@ __device__ __forceinline__ bool get_item(int k, int n_items, int n_bh, int n_qti
     it.empty = false;
     const int idx = (k & 1) ? k * G + (G - 1 - c) : k * G + c;     // boustrophedon deal
     if (idx >= n_items) return false;
-    // Heads are taken in groups of gq.group (reused here as "heads per group"): within a group the
-    // list runs query tile by query tile over the group's heads, so the K and V that the CTAs
-    // stream at any one time belong to one group and stay in L2.
-    const int per_group = gq.group * n_qtiles;
-    const int gi = idx / per_group, rem = idx - gi * per_group;
-    const int h0 = gi * gq.group, hin = min(gq.group, n_bh - h0);
-    const int qrank = rem / hin;
+    // GROUPED: heads are taken in groups of gq.group (reused here as "heads per group"); within a
+    // group the list runs query tile by query tile over the group's heads, so the K and V that the
+    // CTAs stream at any one time belong to one group and stay in L2.  A separate instance, because
+    // the extra index arithmetic (and the code it adds to every role) costs short work items 4-6 %.
+    int qrank;
+    if constexpr (GROUPED) {
+        const int per_group = gq.group * n_qtiles;
+        const int gi = idx / per_group, rem = idx - gi * per_group;
+        const int h0 = gi * gq.group, hin = min(gq.group, n_bh - h0);
+        qrank = rem / hin;
+        it.bh = h0 + rem - qrank * hin;
+    } else {
+        qrank = idx / n_bh;
+        it.bh = idx % n_bh;
+    }
     const int qt = CAUSAL ? (n_qtiles - 1 - qrank) : qrank;
-    it.bh = h0 + rem - qrank * hin;
     it.q_start = qt * kBM;
     const int kv_len = CAUSAL ? min(seq_len, it.q_start + kBM) : seq_len;
     it.n_kv = (kv_len + kBN - 1) / kBN;
@@ -200,7 +197,7 @@ __device__ __forceinline__ bool get_item(int k, int n_items, int n_bh, int n_qti
 // 16-bit kind with P in fp16, because an e4m3 P (3 mantissa bits) misses the output tolerance.
 // The Q and K scales fold into the softmax scale, the V scale into the final normalisation;
 // the output is bf16.
-template <int D, bool CAUSAL, bool BF16, bool FP8, bool GQA>
+template <int D, bool CAUSAL, bool BF16, bool FP8, bool GQA, bool GROUPED>
 __global__ void __launch_bounds__(kThreads, 1)
 prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o,
@@ -321,7 +318,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             bool ok = true;
             for (int r = 0; ok && r < n_rounds; r++) {
                 Item it;
-                if (!get_item<CAUSAL, GQA>(r, n_items, n_bh, n_qtiles, seq_len, gq, it)) continue;
+                if (!get_item<CAUSAL, GQA, GROUPED>(r, n_items, n_bh, n_qtiles, seq_len, gq, it)) continue;
                 if (it_n > 0 && !mbar_wait(smem_u32(&bar_qe), (it_n - 1) & 1, ctl, kBarQEmpty)) break;
                 if constexpr (GQA) {
                     // the box holds only the live rows (token-major); the rest of the tile stays zero
@@ -358,7 +355,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             bool ok = true;
             for (int r = 0; ok && r < n_rounds; r++) {
                 Item it;
-                if (!get_item<CAUSAL, GQA>(r, n_items, n_bh, n_qtiles, seq_len, gq, it)) continue;
+                if (!get_item<CAUSAL, GQA, GROUPED>(r, n_items, n_bh, n_qtiles, seq_len, gq, it)) continue;
                 for (int j = 0; j < it.n_kv; j++, g++) {
                     if constexpr (FP8) {
                         // e4m3 V lands in its own buffers; warps 12-15 turn it into the fp16 operand.
@@ -422,7 +419,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         bool ok = true;
         for (int r = 0; ok && r < n_rounds; r++) {
             Item it;
-            if (!get_item<CAUSAL, GQA>(r, n_items, n_bh, n_qtiles, seq_len, gq, it)) continue;
+            if (!get_item<CAUSAL, GQA, GROUPED>(r, n_items, n_bh, n_qtiles, seq_len, gq, it)) continue;
             if (!mbar_wait(smem_u32(&bar_qf), it_n & 1, ctl, kBarQFull)) break;
             for (int j = 0; j < it.n_kv; j++, g++) {
                 const int sk = g % NK;
@@ -430,7 +427,6 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                 // the score buffer last held S and then P of tile g - kNU: that P V must be done
                 if (g >= kNU && !mbar_wait(smem_u32(&bar_pvd[(g - kNU) % kRing]), ((g - kNU) / kRing) & 1, ctl, kBarSFree)) { ok = false; break; }
                 tc_fence_after();
-                if (r == 0 && lane == 0) FA_TS(1, j, 0);
                 const uint32_t kb = k_s + sk * L::kKBytes;
                 const uint32_t sc = tmem + u * 128;
                 if constexpr (FP8) {
@@ -452,7 +448,6 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                     if (j == it.n_kv - 1) tc_commit(smem_u32(&bar_qe));   // Q is dead after the item's last Q K^T
                 }
                 __syncwarp();
-                if (r == 0 && lane == 0) FA_TS(1, j, 1);
                 u = (u == kNU - 1) ? 0 : u + 1;
             }
             it_n++;
@@ -465,7 +460,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         bool ok = true;
         for (int r = 0; ok && r < n_rounds; r++) {
             Item it;
-            if (!get_item<CAUSAL, GQA>(r, n_items, n_bh, n_qtiles, seq_len, gq, it)) continue;
+            if (!get_item<CAUSAL, GQA, GROUPED>(r, n_items, n_bh, n_qtiles, seq_len, gq, it)) continue;
             for (int j = 0; j < it.n_kv; j++, g++) {
                 const int sv = g % NV;
                 if (!mbar_wait(smem_u32(&bar_vf[sv]), (g / NV) & 1, ctl, kBarVFull)) { ok = false; break; }
@@ -473,7 +468,6 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                 // the first P V of an item overwrites O: the previous item's epilogue must have read it
                 if (j == 0 && it_n > 0 && !mbar_wait(smem_u32(&bar_ofree), (it_n - 1) & 1, ctl, kBarOFree)) { ok = false; break; }
                 tc_fence_after();
-                if (r == 0 && lane == 0) FA_TS(1, j, 2);
                 const uint32_t vb = v_s + sv * L::kVBytes;
                 const uint32_t pc = tmem + u * 128;         // P overwrote the first 64 columns of the tile's S
 #pragma unroll
@@ -486,7 +480,6 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                     if (j == it.n_kv - 1) tc_commit(smem_u32(&bar_odone));   // the item's O is complete
                 }
                 __syncwarp();
-                if (r == 0 && lane == 0) FA_TS(1, j, 3);
                 if (u == kNU - 1) { u = 0; u_phase ^= 1; } else { u++; }
             }
             it_n++;
@@ -509,7 +502,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         bool ok = true;
         for (int r = 0; ok && r < n_rounds; r++) {
             Item it;
-            if (!get_item<CAUSAL, GQA>(r, n_items, n_bh, n_qtiles, seq_len, gq, it)) {
+            if (!get_item<CAUSAL, GQA, GROUPED>(r, n_items, n_bh, n_qtiles, seq_len, gq, it)) {
                 if constexpr (GQA) {
                     // a KV split past the end of a short sequence: weight zero in the merge
                     if (it.empty && r_in_tile < gq.live_rows && it.tok0 + r_in_tile / gq.group < gq.n_tok) {
@@ -658,7 +651,6 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                 for (int bx = 0; bx < NBOX; bx++)
                     tma_store_3d(&tm_o, o_s + bx * L::kBox, bx * 64, it.q_start, it.bh);
                 tma_store_commit();
-                FA_CTS(it_n * gridDim.x + blockIdx.x, 2);
             }
             it_n++;
         }
@@ -676,7 +668,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
 
         for (int r = 0; ok && r < n_rounds; r++) {
             Item it;
-            if (!get_item<CAUSAL, GQA>(r, n_items, n_bh, n_qtiles, seq_len, gq, it)) continue;
+            if (!get_item<CAUSAL, GQA, GROUPED>(r, n_items, n_bh, n_qtiles, seq_len, gq, it)) continue;
             const int row = it.q_start + r_in_tile;
             // keys [0,row_limit) visible.  Decode with several query tokens: they are the last n_tok
             // entries of the cache, token t sees everything up to and including itself.
@@ -694,7 +686,6 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             // one agreed sequence.
             float m_mine = -1e30f;
             uint64_t lsum2 = pack2(0.0f, 0.0f);
-            if (tid == 0) FA_CTS(it_n * gridDim.x + blockIdx.x, 0);
 
             for (int j = (g0 & 1) == grp ? 0 : 1; j < it.n_kv; j += 2) {
                 const int g = g0 + j;                     // global tile index; g & 1 == grp
@@ -702,7 +693,6 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                 // The votes keep the warp together: every lane leaves the loop or none does.
                 if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&bar_qk[g % kRing]), (g / kRing) & 1, ctl, kBarSFull))) { ok = false; break; }
                 tc_fence_after();
-                if ((tid & 127) == 0 && r == 0) FA_TS(grp * 2, j, 0);
                 const int u = g % kNU;                    // the tile's score buffer; P goes back into its first half
                 const uint32_t t_s = tmem + lane_off + u * 128;
                 if constexpr (GQA) {
@@ -718,7 +708,6 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                 }
                 uint32_t s[128];
                 tmem_ld128_wait(t_s, s);
-                if ((tid & 127) == 0 && r == 0) FA_TS(grp * 2, j, 1);
                 if ((tile_min_limit - kv_start) < kBN) { // tile touches the mask or the ragged end
                     const int limit = row_limit - kv_start;   // columns [0,limit) are visible
 #pragma unroll
@@ -742,15 +731,17 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                 if (j > 0) {
                     // poll for the previous tile's entry (normally long there); bounded like every wait
                     uint32_t mb = 0, tag = 0;
-                    bool got = false;
-                    for (uint32_t spin = 0; ; spin++) {
-                        asm volatile("ld.volatile.shared.v2.b32 {%0, %1}, [%2];" : "=r"(mb), "=r"(tag) : "r"(slot));
-                        if (tag == static_cast<uint32_t>(g - 1)) { got = true; break; }
-                        if ((spin & 0xFFu) == 0xFFu && (*ctl.abort_flag || spin > (1u << 26))) break;
-                    }
-                    if (!__all_sync(0xffffffffu, got)) {
-                        *ctl.abort_flag = 1;
-                        atomicCAS(ctl.status, 0, (kErrWaitTimeout << 16) | kBarM);
+                    const int w = bounded_wait(
+                        [&] {
+                            asm volatile("ld.volatile.shared.v2.b32 {%0, %1}, [%2];" : "=r"(mb), "=r"(tag) : "r"(slot));
+                            return tag == static_cast<uint32_t>(g - 1);
+                        },
+                        [&] { return *ctl.abort_flag != 0; }, [] { return global_timer_ns(); }, kWaitLimitNs, 256u);
+                    if (!__all_sync(0xffffffffu, w == kWaitDone)) {
+                        if (w == kWaitTimedOut) {
+                            *ctl.abort_flag = 1;
+                            atomicCAS(ctl.status, 0, wait_timeout_word(kBarM));
+                        }
                         ok = false;
                         break;
                     }
@@ -765,7 +756,6 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                     const float f = ex2_approx(m_mine - m_new);
                     lsum2 = fma2(lsum2, pack2(f, f), pack2(0.0f, 0.0f));
                 }
-                if ((tid & 127) == 0 && r == 0) FA_TS(grp * 2, j, 2);
 
                 // ---- rare: the max in use grew -> rescale O in TMEM before this tile's P V
                 if (__any_sync(0xffffffffu, changed)) {
@@ -817,16 +807,13 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                         tmem_st_x16(t_s + c * PAIRS + q * 16, *reinterpret_cast<uint32_t (*)[16]>(&pk[q * 16]));
                 }
                 lsum2 = add2(add2(acc0, acc1), add2(acc2, acc3));
-                if ((tid & 127) == 0 && r == 0) FA_TS(grp * 2, j, 3);
                 tmem_wait_st();
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(smem_u32(&bar_pf[u]));
-                if ((tid & 127) == 0 && r == 0) FA_TS(grp * 2, j, 4);
             }
             if (!ok) break;
 
-            if (tid == 0) FA_CTS(it_n * gridDim.x + blockIdx.x, 1);
             {
                 // ---- end of the item: hand (reference max, partial row sum) to the epilogue warps and
                 // go straight on to the next item
@@ -866,19 +853,21 @@ template <int D, bool CAUSAL, bool BF16, bool FP8>
 int launch_instance(const fa_prefill_args& a, DeviceState* st, const CUtensorMap& tq,
                     const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& to) {
     using L = PrefillSmem<D, FP8>;
-    auto kernel = prefill_kernel<D, CAUSAL, BF16, FP8, false>;
-    static bool configured[64] = {};
-    if (!configured[st->device]) {
-        FA_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
-        configured[st->device] = true;
-    }
     const int n_bh = a.batch_size * a.num_heads;
+    GqaDev order{};
+    order.group = heads_per_group(n_bh, a.seq_len, a.d_head, FP8 ? 1 : 2);
+    const bool grouped = order.group < n_bh;
+    auto kernel = grouped ? prefill_kernel<D, CAUSAL, BF16, FP8, false, true>
+                          : prefill_kernel<D, CAUSAL, BF16, FP8, false, false>;
+    static bool configured[64][2] = {};
+    if (!configured[st->device][grouped]) {
+        FA_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
+        configured[st->device][grouped] = true;
+    }
     const int n_qtiles = (a.seq_len + kBM - 1) / kBM;
     const long long n_items = (long long)n_bh * n_qtiles;
     if (n_items > 0x7FFFFFFFll) return FA_ERR_INVALID_ARGUMENT;
     const unsigned grid = (unsigned)(n_items < st->sm_count ? n_items : st->sm_count);
-    GqaDev order{};
-    order.group = heads_per_group(n_bh, a.seq_len, a.d_head, FP8 ? 1 : 2);
     kernel<<<grid, kThreads, L::kTotal, static_cast<cudaStream_t>(a.stream)>>>(
         tq, tk, tv, to, a.lse, a.seq_len, n_bh, n_qtiles, (int)n_items, a.scale * kLog2e, a.q_scale,
         a.k_scale, a.v_scale, st->status, order);
@@ -890,7 +879,7 @@ template <int D, bool BF16, bool FP8>
 int launch_gqa_instance(const GqaLaunch& g, DeviceState* st, const CUtensorMap& tq, const CUtensorMap& tk,
                         const CUtensorMap& tv) {
     using L = PrefillSmem<D, FP8>;
-    auto kernel = prefill_kernel<D, false, BF16, FP8, true>;
+    auto kernel = prefill_kernel<D, false, BF16, FP8, true, false>;
     static bool configured[64] = {};
     if (!configured[st->device]) {
         FA_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
@@ -979,14 +968,6 @@ int launch_decode_gqa(const GqaLaunch& g, DeviceState* st) {
     return bf ? launch_gqa_instance<128, true, false>(g, st, tq, tk, tv) : launch_gqa_instance<128, false, false>(g, st, tq, tk, tv);
 }
 
-#ifdef FA_PHASE_TIMING
-extern "C" __attribute__((visibility("default"))) int fa_debug_phase_ts(long long* out) {
-    return (int)cudaMemcpyFromSymbol(out, g_phase_ts, sizeof(long long) * 3 * 64 * 8);
-}
-extern "C" __attribute__((visibility("default"))) int fa_debug_cta_ts(long long* out) {
-    return (int)cudaMemcpyFromSymbol(out, g_cta_ts, sizeof(long long) * 4096 * 8);
-}
-#endif
 
 // e4m3 inputs (d_head 128), bf16 output.
 int launch_prefill_fp8(const fa_prefill_args& a, DeviceState* st) {

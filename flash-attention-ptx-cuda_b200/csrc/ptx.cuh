@@ -16,16 +16,12 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 
+#include "bounded_wait.h"
+
 namespace fa {
 
 constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // 2 s per wait
 constexpr uint32_t kParkNs = 20000;                         // suspend-time hint of one poll of a waiting thread
-
-// Error words written to the device status buffer: (code << 16) | detail.
-enum : int {
-    kErrNone        = 0,
-    kErrWaitTimeout = 1,   // an mbarrier wait ran out of time; detail = barrier id
-};
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -87,26 +83,20 @@ struct WaitCtl {
 };
 
 // Waits for the phase with the given parity to complete.  Returns false if the
-// CTA is aborting (this waiter timed out, or another one did).
+// CTA is aborting (this waiter timed out, or another one did).  The loop itself is
+// bounded_wait() (bounded_wait.h), which a host test drives through its give-up branch.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const WaitCtl& ctl,
                                           int barrier_id) {
     if (mbar_try_wait(bar, parity)) return true;
-    unsigned long long t0 = 0;
-    uint32_t spins = 0;
-    while (!mbar_try_wait_parked(bar, parity, kParkNs)) {
-        if ((++spins & 0xFu) == 0) {
-            if (*ctl.abort_flag) return false;
-            const unsigned long long now = global_timer_ns();
-            if (t0 == 0) {
-                t0 = now;
-            } else if (now - t0 > kWaitLimitNs) {
-                *ctl.abort_flag = 1;
-                atomicCAS(ctl.status, 0, (kErrWaitTimeout << 16) | (barrier_id & 0xFFFF));
-                return false;
-            }
-        }
+    const int r = bounded_wait([&] { return mbar_try_wait_parked(bar, parity, kParkNs); },
+                               [&] { return *ctl.abort_flag != 0; }, [] { return global_timer_ns(); },
+                               kWaitLimitNs, 16u);
+    if (r == kWaitDone) return true;
+    if (r == kWaitTimedOut) {
+        *ctl.abort_flag = 1;
+        atomicCAS(ctl.status, 0, wait_timeout_word(barrier_id));
     }
-    return true;
+    return false;
 }
 
 // ---------------------------------------------------------------------------

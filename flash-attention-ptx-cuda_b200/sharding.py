@@ -8,8 +8,9 @@ Two ways the path shards, and only these two:
 * by KV sequence, for one long cache: each rank holds a contiguous slice of the
   keys, runs split-KV decode on it and contributes a normalised fp32 partial O
   with its LSE; ONE all-gather of ``[B*H, D+1]`` floats per rank brings all
-  partials into local memory, where ``fa_combine`` merges them
-  (``kv_shard``, ``gather_partials``, ``sharded_decode``).
+  partials into local memory, where the merge kernel reads them in place
+  (``kv_shard``, ``ShardedDecode`` over ``fa_decode_kv_sharded``; ``gather_partials``
+  is the same exchange through ``torch.distributed`` for host-side tests).
 
 The reference is single-GPU (no NCCL/MPI call site exists in it); the exchange
 step is defined by the LSE-merge identity its attention satisfies.
@@ -51,8 +52,15 @@ def gather_partials(o_f32, lse, group=None):
 
 
 class ShardedDecode:
-    """KV-sequence-sharded decode on this rank's GPU: fa_decode on the local key slice,
-    one all-gather, fa_combine.  Buffers are allocated once and reused."""
+    """KV-sequence-sharded decode on this rank's GPU through ``fa_decode_kv_sharded``: split-KV
+    decode on the local key slice, whose merge writes the rank's packed ``[BH, D+1]`` block into
+    the all-gather's receive buffer; one in-place ``ncclAllGather``; ``fa_combine_packed`` on the
+    gathered blocks.  Four launches on one stream, no copies in between.
+
+    The library talks to NCCL itself (its own communicator, one rank per GPU); the id travels
+    over the existing ``torch.distributed`` group, which is used for nothing else.  Buffers are
+    allocated once and reused.  A rank whose slice is empty (``local_kv == 0``) contributes
+    weight zero.  Call ``close()`` (or use as a context manager) to destroy the communicator."""
 
     def __init__(self, fa, batch_size, num_heads, d_head, local_kv, dtype="f16", num_splits=0, group=None):
         import torch
@@ -61,32 +69,42 @@ class ShardedDecode:
         self.b, self.h, self.d, self.dtype = batch_size, num_heads, d_head, dtype
         self.bh = batch_size * num_heads
         self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
         dev = torch.device("cuda", torch.cuda.current_device())
         self.splits = num_splits or fa.decode_default_splits(batch_size, num_heads, max(local_kv, 1))
         self.ws_bytes = fa.decode_workspace_bytes(batch_size, num_heads, d_head, self.splits)
         self.ws = torch.empty(self.ws_bytes, device=dev, dtype=torch.uint8)
-        self.packed = torch.empty((self.bh, d_head + 1), device=dev, dtype=torch.float32)
-        self.o_local = torch.empty((self.bh, d_head), device=dev, dtype=torch.float32)
-        self.lse_local = torch.empty((self.bh,), device=dev, dtype=torch.float32)
-        self.gathered_flat = torch.empty((self.world * self.bh, d_head + 1), device=dev, dtype=torch.float32)
-        self.gathered = self.gathered_flat.view(self.world, self.bh, d_head + 1)
-        self.o_parts = torch.empty((self.world, self.bh, d_head), device=dev, dtype=torch.float32)
-        self.lse_parts = torch.empty((self.world, self.bh), device=dev, dtype=torch.float32)
+        self.gather_bytes = fa.decode_kv_sharded_gather_bytes(batch_size, num_heads, d_head, self.world)
+        self.gathered = torch.empty((self.world, self.bh, d_head + 1), device=dev, dtype=torch.float32)
+        ids = [fa.nccl_unique_id() if self.rank == 0 else None]
+        dist.broadcast_object_list(ids, src=dist.get_global_rank(group, 0) if group is not None else 0, group=group)
+        self.comm = fa.nccl_comm_create(self.world, ids[0], self.rank)
 
     def __call__(self, q, k_local, v_local, o, lse, scale, stream=None):
         """q [BH, D]; k_local, v_local [BH, local_kv, D]; o [BH, D] 16-bit, lse [BH] fp32 (outputs,
-        identical on every rank).  Enqueues on the current torch stream."""
+        identical on every rank).  Everything is enqueued on ``stream`` (default: the current
+        torch stream)."""
         import torch
-        import torch.distributed as dist
         stream = stream or torch.cuda.current_stream()
         local_kv = k_local.shape[1]
-        self.fa.decode(q, k_local, v_local, None, self.lse_local, self.o_local, self.b, self.h, local_kv,
-                       self.d, float(scale), dtype=self.dtype, num_splits=self.splits, workspace=self.ws,
-                       workspace_bytes=self.ws_bytes, stream=stream)
-        self.packed[:, :self.d].copy_(self.o_local)
-        self.packed[:, self.d].copy_(self.lse_local)
-        dist.all_gather_into_tensor(self.gathered_flat, self.packed, group=self.group)
-        self.o_parts.copy_(self.gathered[:, :, :self.d])
-        self.lse_parts.copy_(self.gathered[:, :, self.d])
-        self.fa.combine(self.o_parts, self.lse_parts, self.world, self.bh, self.d, o, lse,
-                        dtype=self.dtype, stream=stream)
+        rc = self.fa.decode_kv_sharded_raw(q, k_local, v_local, o, lse, self.b, self.h, local_kv, self.d,
+                                           float(scale), self.comm, self.gathered, self.gather_bytes,
+                                           dtype=self.dtype, num_splits=self.splits if local_kv else 0,
+                                           workspace=self.ws, workspace_bytes=self.ws_bytes, stream=stream)
+        if rc != self.fa.FA_OK:
+            raise self.fa.FaError(rc, "fa_decode_kv_sharded")
+
+    LAUNCHES_PER_STEP = 4          # split partials, their merge, the all-gather, the cross-rank merge
+
+    def close(self):
+        if getattr(self, "comm", None):
+            import torch
+            torch.cuda.synchronize()
+            self.fa.nccl_comm_destroy(self.comm)
+            self.comm = None
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        self.close()

@@ -38,6 +38,7 @@ extern "C" {
 #define FA_ERR_CUDA             (-5)  /* a CUDA runtime/driver call failed; see fa_last_cuda_error() */
 #define FA_ERR_DEVICE_TIMEOUT   (-6)  /* a kernel gave up on a bounded wait; see fa_device_status() */
 #define FA_ERR_NOT_SM100        (-7)  /* the current device is not compute capability 10.x */
+#define FA_ERR_NCCL             (-8)  /* an NCCL call failed, or libnccl.so.2 could not be loaded */
 
 enum { FA_DTYPE_F16 = 0, FA_DTYPE_BF16 = 1, FA_DTYPE_E4M3 = 2 };
 
@@ -302,6 +303,42 @@ int fa_combine(const float* o_parts, const float* lse_parts, int n_parts, int ro
                void* o, float* lse, int dtype, void* stream);
 
 /*
+ * The same merge over PACKED partials: packed_parts is fp32 [n_parts, rows, d_head + 1], a row
+ * holding the normalised partial O followed by its LSE - exactly the receive buffer of one
+ * all-gather of every rank's [rows, d_head + 1] block, read where it lies (no unpacking pass).
+ */
+int fa_combine_packed(const float* packed_parts, int n_parts, int rows, int d_head, void* o,
+                      float* lse, int dtype, void* stream);
+
+/*
+ * KV-sequence-sharded decode, the one multi-GPU path with an exchange step (the reference is
+ * single-GPU; the definition is src/demo.cu:28-70 on the whole cache, which the LSE merge of
+ * per-slice results reproduces).  Every rank holds a contiguous slice of the keys of ALL heads
+ * and calls this with the same batch_size / num_heads / d_head / dtype:
+ *     1. split-KV decode on the local slice (args->k, args->v, args->seq_len_kv = local keys;
+ *        0 is allowed: the rank then contributes weight zero), whose merge writes this rank's
+ *        packed [rows, d_head + 1] block straight into its place in `gather`;
+ *     2. ONE ncclAllGather, in place, of that block (rows * (d_head + 1) floats per rank);
+ *     3. fa_combine_packed over the gathered blocks -> args->o (16-bit) and args->lse, the
+ *        same on every rank.
+ * All on args->stream: partial kernel, merge kernel, all-gather, merge kernel (4 launches).
+ * nccl_comm is the caller's ncclComm_t (one rank per GPU); gather is device memory of
+ * fa_decode_kv_sharded_gather_bytes(...) bytes, reusable across calls; args->workspace as
+ * for fa_decode; args->o_f32 is ignored.  NCCL is loaded at run time (libnccl.so.2 - the
+ * copy already in the process, if any), the library does not link against it.
+ *
+ * fa_nccl_unique_id / fa_nccl_comm_create / fa_nccl_comm_destroy forward to
+ * ncclGetUniqueId / ncclCommInitRank / ncclCommDestroy of that same NCCL, for bindings
+ * that cannot include <nccl.h> (the id is 128 bytes; rank 0 creates it and hands it to the
+ * others by any side channel).
+ */
+size_t fa_decode_kv_sharded_gather_bytes(int batch_size, int num_heads, int d_head, int n_ranks);
+int    fa_decode_kv_sharded(const fa_decode_args* args, void* nccl_comm, float* gather, size_t gather_bytes);
+int    fa_nccl_unique_id(void* id_out, size_t id_bytes);
+int    fa_nccl_comm_create(void** comm_out, int n_ranks, const void* id, size_t id_bytes, int rank);
+int    fa_nccl_comm_destroy(void* comm);
+
+/*
  * Tensor-core known-answer test (the role of test_ptx_mma in the reference,
  * src/bench.cu:51-165, for the tcgen05 path): one CTA computes
  *   S = Q K^T            (Q [128,d_head], K [128,d_head], 16-bit, from host)
@@ -320,6 +357,8 @@ int fa_kat(int dtype, int d_head, const void* q_host, const void* k_host, const 
  * wait timed out, detail = barrier id).  Synchronises the device.
  */
 int         fa_device_status(int* status_word);
+/* The return code fa_device_status / fa_prefill_host derive from a status word (no device access). */
+int         fa_status_word_to_error(int status_word);
 int         fa_clear_device_status(void);
 const char* fa_error_string(int code);
 const char* fa_last_cuda_error(void);

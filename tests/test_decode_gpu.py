@@ -93,6 +93,92 @@ def test_combine_merges_rank_partials(fa, dev, oracle):
     assert np.abs(dl.cpu().numpy() - lm).max() < 1e-5
 
 
+def test_combine_packed_reads_the_gathered_buffer_in_place(fa, dev, oracle):
+    """fa_combine_packed on [ranks, rows, D + 1] blocks (normalised O then LSE per row), the layout one
+    all-gather of packed rows produces; an empty rank (LSE = -inf) must carry weight zero."""
+    import torch
+    bh, skv, d, ranks = 6, 3000, 64, 3
+    scale = 0.125
+    k, v = (oracle.round_to(x, "f16") for x in oracle.normal_inputs(90, (bh, skv, d), n=2))
+    q = oracle.round_to(oracle.normal_inputs(91, (bh, 1, d), n=1)[0], "f16")
+    per = skv // ranks
+    packed = np.zeros((ranks + 1, bh, d + 1), np.float32)
+    for r in range(ranks):
+        _, l, of = _run_decode(fa, dev, q, k[:, r * per:(r + 1) * per], v[:, r * per:(r + 1) * per],
+                               scale, "f16", 2, want_f32=True)
+        packed[r, :, :d] = of
+        packed[r, :, d] = l
+    packed[ranks, :, :d] = 123.0                              # a rank without keys: must not contribute
+    packed[ranks, :, d] = -np.inf
+    g = torch.from_numpy(packed).to(dev)
+    do = torch.zeros((bh, d), device=dev, dtype=torch.float16)
+    dl = torch.zeros((bh,), device=dev, dtype=torch.float32)
+    fa.combine_packed(g, ranks + 1, bh, d, do, dl, dtype="f16")
+    torch.cuda.synchronize()
+    o_ref, l_ref = oracle.attention(q, k, v, scale, False)
+    assert np.abs(do.float().cpu().numpy() - o_ref[:, 0]).max() < TOL_O
+    assert np.abs(dl.cpu().numpy() - l_ref[:, 0]).max() < TOL_LSE
+
+
+def test_kv_sharded_entry_on_a_one_rank_communicator(fa, dev, oracle):
+    """fa_decode_kv_sharded end to end on one GPU: an NCCL communicator of one rank (created through
+    the library's own NCCL binding), the packed partial written in place, the in-place all-gather and
+    the packed merge.  With one rank the result must equal plain fa_decode's."""
+    import torch
+    bh, skv, d = 8, 5000, 128
+    scale = float(1.0 / np.sqrt(np.float32(d)))
+    k, v = (oracle.round_to(x, "f16") for x in oracle.normal_inputs(92, (bh, skv, d), n=2))
+    q = oracle.round_to(oracle.normal_inputs(93, (bh, 1, d), n=1)[0], "f16")
+    dq = torch.from_numpy(q.reshape(bh, d)).to(dev, torch.float16)
+    dk, dv = (torch.from_numpy(x).to(dev, torch.float16) for x in (k, v))
+    comm = fa.nccl_comm_create(1, fa.nccl_unique_id(), 0)
+    try:
+        splits = 4
+        wsb = fa.decode_workspace_bytes(1, bh, d, splits)
+        ws = torch.empty(wsb, device=dev, dtype=torch.uint8)
+        gb = fa.decode_kv_sharded_gather_bytes(1, bh, d, 1)
+        gather = torch.full((gb // 4,), float("nan"), device=dev, dtype=torch.float32)
+        do = torch.full((bh, d), float("nan"), device=dev, dtype=torch.float16)
+        dl = torch.full((bh,), float("nan"), device=dev, dtype=torch.float32)
+        for _ in range(2):                                    # buffers are reused across calls
+            rc = fa.decode_kv_sharded_raw(dq, dk, dv, do, dl, 1, bh, skv, d, scale, comm, gather, gb,
+                                          num_splits=splits, workspace=ws, workspace_bytes=wsb)
+            assert rc == 0, fa.last_cuda_error()
+        torch.cuda.synchronize()
+        o_ref, l_ref = oracle.attention(q, k, v, scale, False)
+        assert np.abs(do.float().cpu().numpy() - o_ref[:, 0]).max() < TOL_O
+        assert np.abs(dl.cpu().numpy() - l_ref[:, 0]).max() < TOL_LSE
+        o_plain, l_plain, _ = _run_decode(fa, dev, q, k, v, scale, "f16", splits)
+        assert np.array_equal(do.float().cpu().numpy(), o_plain) and np.array_equal(dl.cpu().numpy(), l_plain)
+        # too small a receive buffer is refused before anything is launched
+        assert fa.decode_kv_sharded_raw(dq, dk, dv, do, dl, 1, bh, skv, d, scale, comm, gather, gb - 4,
+                                        num_splits=splits, workspace=ws, workspace_bytes=wsb) == fa.FA_ERR_WORKSPACE
+    finally:
+        fa.nccl_comm_destroy(comm)
+
+
+def test_decode_many_heads(fa, dev, oracle):
+    """batch * heads beyond 65535 (the limit of a grid's second dimension; the kernel's grid is
+    one-dimensional)."""
+    import torch
+    bh, skv, d = 70000, 48, 64
+    g = torch.Generator(device=dev).manual_seed(5)
+    dq = torch.randn((bh, d), device=dev, generator=g).half()
+    dk = torch.randn((bh, skv, d), device=dev, generator=g).half()
+    dv = torch.randn((bh, skv, d), device=dev, generator=g).half()
+    do = torch.empty((bh, d), device=dev, dtype=torch.float16)
+    dl = torch.empty((bh,), device=dev, dtype=torch.float32)
+    wsb = fa.decode_workspace_bytes(1, bh, d, 1)
+    ws = torch.empty(wsb, device=dev, dtype=torch.uint8)
+    fa.decode(dq, dk, dv, do, dl, None, 1, bh, skv, d, 0.125, num_splits=1, workspace=ws, workspace_bytes=wsb)
+    torch.cuda.synchronize()
+    heads = [0, 65535, 65536, 69999]
+    o_ref, l_ref = oracle.attention(dq[heads].float().cpu().numpy()[:, None], dk[heads].float().cpu().numpy(),
+                                    dv[heads].float().cpu().numpy(), 0.125, False)
+    assert np.abs(do[heads].float().cpu().numpy() - o_ref[:, 0]).max() < TOL_O
+    assert np.abs(dl[heads].cpu().numpy() - l_ref[:, 0]).max() < TOL_LSE
+
+
 def test_decode_rejects_small_workspace(fa, dev):
     import torch
     t = torch.zeros(4096, device=dev, dtype=torch.float16)

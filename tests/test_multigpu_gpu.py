@@ -1,6 +1,6 @@
 """Two ranks, one GPU each, NCCL: (batch x head)-sharded prefill gives bit-identical
-heads to the single-GPU run, and KV-sequence-sharded decode (fa_decode on the local
-slice -> one all-gather -> fa_combine) matches the unsharded oracle.
+heads to the single-GPU run, and KV-sequence-sharded decode (fa_decode_kv_sharded: the
+local slice -> one in-place all-gather -> packed merge) matches the unsharded oracle.
 Skipped on machines with fewer than two GPUs."""
 import os
 import sys
@@ -47,10 +47,10 @@ def _worker(rank, world, port, q_out):
         dv = torch.from_numpy(vv[:, k0:k0 + kc]).to(dev, torch.float16).contiguous()
         do = torch.zeros((bh, d), device=dev, dtype=torch.float16)
         dl = torch.zeros((bh,), device=dev, dtype=torch.float32)
-        run = sh.ShardedDecode(fa, 1, bh, d, kc, dtype="f16", num_splits=3)
-        run(dq, dk, dv, do, dl, scale)
-        run(dq, dk, dv, do, dl, scale)                     # buffers are reused across calls
-        torch.cuda.synchronize()
+        with sh.ShardedDecode(fa, 1, bh, d, kc, dtype="f16", num_splits=3) as run:
+            run(dq, dk, dv, do, dl, scale)
+            run(dq, dk, dv, do, dl, scale)                 # buffers are reused across calls
+            torch.cuda.synchronize()
         o2_ref, l2_ref = oracle.attention(qq, kk, vv, scale, False)
         e2 = float(max(np.abs(do.float().cpu().numpy() - o2_ref[:, 0]).max() / 2e-3,
                        np.abs(dl.cpu().numpy() - l2_ref[:, 0]).max() / 1e-3))
