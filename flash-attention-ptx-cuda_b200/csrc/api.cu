@@ -44,9 +44,11 @@ DeviceState* device_state() {
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
     DeviceState* st = &g_states[dev];
-    if (st->device == dev) return st;
+    // `ready` is release-stored after the fields and acquire-loaded before them, so a thread that
+    // sees it set also sees the fields (several host threads may make the first call at once)
+    if (st->ready.load(std::memory_order_acquire)) return st;
     std::lock_guard<std::mutex> lock(g_mutex);
-    if (st->device == dev) return st;
+    if (st->ready.load(std::memory_order_relaxed)) return st;
     int sms = 0, major = 0;
     if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return nullptr;
     if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess) return nullptr;
@@ -65,6 +67,7 @@ DeviceState* device_state() {
     st->cc_major = major;
     st->status   = status;
     st->device   = dev;
+    st->ready.store(true, std::memory_order_release);
     return st;
 }
 
@@ -179,6 +182,8 @@ FA_EXPORT int fa_prefill_host(const fa_prefill_args* h) {
     if (rc != FA_OK) return rc;
     DeviceState* st = device_state();
     if (!st) return FA_ERR_CUDA;
+    // the staging buffers and the three streams belong to the device: one host call at a time
+    std::lock_guard<std::mutex> host_lock(st->host_entry_mutex);
     const size_t bh    = (size_t)h->batch_size * h->num_heads;
     const size_t elems = bh * h->seq_len * h->d_head;
     const size_t in_b  = elems * (h->dtype == FA_DTYPE_E4M3 ? 1 : 2);

@@ -12,6 +12,8 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 
+#include <mutex>
+
 #include "../../include/fa_b200.h"
 
 #define FA_EXPORT extern "C" __attribute__((visibility("default")))
@@ -19,6 +21,8 @@
 namespace fa {
 
 struct DeviceState {
+    std::atomic<bool> ready{false};  // set last, with release order, by the thread that filled the fields in
+    std::mutex host_entry_mutex;     // serialises fa_prefill_host calls on this device (shared staging and streams)
     int    device      = -1;
     int    sm_count    = 0;
     int    cc_major    = 0;

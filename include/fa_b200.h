@@ -97,7 +97,9 @@ int fa_set_prefill_variant(int variant);
  * buffers are kept per device and grown on demand.  Large inputs are cut into
  * chunks of heads that flow through three internal streams, so the copies in
  * both PCIe directions and the kernels overlap; use pinned host memory to
- * benefit.  `stream` is ignored.
+ * benefit.  `stream` is ignored.  Calls on the same device are serialised inside the
+ * library (they share the staging buffers and streams); calls on different devices run
+ * concurrently.
  */
 int fa_prefill_host(const fa_prefill_args* args_with_host_pointers);
 
@@ -162,8 +164,11 @@ int    fa_decode(const fa_decode_args* args);
  * launches nothing and returns FA_ERR_WORKSPACE.  Lower num_splits to fit.
  *
  * The first call on each device looks up the array's device address (once,
- * with that device current); make that first call before starting any stream
- * capture.  All calls on a device share the one array: it still holds the
+ * with that device current); make that first call during start-up and before
+ * starting any stream capture: with CUDA's lazy module loading that lookup can
+ * be the moment the driver loads this library's device code and backs the
+ * array with memory, which is the driver's allocation, not the library's, and
+ * happens once.  Every later call only launches kernels.  All calls on a device share the one array: it still holds the
  * previous call's partials (every slot a call reads is first written by that
  * call, so nothing needs clearing), and two calls whose kernels overlap on the
  * GPU - different streams, or different host threads - race on it.  Serialise

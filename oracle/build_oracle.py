@@ -27,7 +27,8 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(HERE)
 REF_OUT = os.path.join(HERE, "_ref")
-REFERENCE = os.environ.get("FA_REFERENCE_DIR", "/root/reference")
+# the reference checkout: FA_REFERENCE_DIR, else a directory "reference" next to this repository
+REFERENCE = os.environ.get("FA_REFERENCE_DIR") or os.path.join(os.path.dirname(ROOT), "reference")
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 
 # Itanium-mangled name of cpu_attention(const float*, const float*, const float*,

@@ -37,7 +37,8 @@ sys.path.insert(0, ROOT)
 
 from oracle import oracle  # noqa: E402
 
-REFERENCE = os.environ.get("FA_REFERENCE_DIR", "/root/reference")
+# the reference checkout: FA_REFERENCE_DIR, else a directory "reference" next to this repository
+REFERENCE = os.environ.get("FA_REFERENCE_DIR") or os.path.join(os.path.dirname(ROOT), "reference")
 
 
 def read_dump(path: str) -> np.ndarray:

@@ -71,11 +71,38 @@ def test_static_scratch_default_splits(fa, dev, oracle):
 
 
 def test_static_scratch_rejects_oversized_problem(fa, dev):
-    """16384 heads-x-splits at d_head 128 fit (8.45 MB); twice that does not, and the call
-    must refuse on the host without launching."""
+    """16384 heads-x-splits at d_head 128 fit (8.45 MB); 2048 heads x 16 splits (16.9 MB of
+    partials) do not, and the call must refuse on the host without launching.  The buffers are
+    sized honestly for that problem (16 keys per head), so if the check ever regressed the result
+    would be a wrong answer, not an out-of-bounds access."""
     import torch
-    t = torch.zeros(1024, device=dev, dtype=torch.float16)
-    # 2048 heads x 16 splits x 129 floats = 16.9 MB > FA_DECODE_STATIC_SCRATCH_BYTES
-    rc = fa.decode_static_raw(t, t, t, t, None, None, 64, 32, 16384, 128, 0.1, num_splits=16)
+    bh, skv, d = 2048, 16, 128
+    q = torch.zeros((bh, d), device=dev, dtype=torch.float16)
+    k = torch.zeros((bh, skv, d), device=dev, dtype=torch.float16)
+    v = torch.zeros((bh, skv, d), device=dev, dtype=torch.float16)
+    o = torch.full((bh, d), 7.0, device=dev, dtype=torch.float16)
+    rc = fa.decode_static_raw(q, k, v, o, None, None, 64, 32, skv, d, 0.1, num_splits=16)
     assert rc == fa.FA_ERR_WORKSPACE
+    torch.cuda.synchronize()
+    assert (o == 7.0).all()                                   # nothing ran
     assert 2048 * 16 * 129 * 4 > fa.DECODE_STATIC_SCRATCH_BYTES >= 1024 * 16 * 129 * 4
+
+
+def test_static_scratch_calls_leave_free_device_memory_unchanged(fa, dev, oracle):
+    """The reason the entry point exists: after the first call on a device (which resolves the
+    built-in array's address, and may be when the driver loads the library's device code), a call
+    takes no device memory and gives none back."""
+    import torch
+    bh, skv, d = 8, 2048, 128
+    scale = float(1.0 / np.sqrt(np.float32(d)))
+    _, _, _, (dq, dk, dv) = _inputs(oracle, 930, bh, skv, d, "f16", dev)
+    o = torch.empty((bh, d), device=dev, dtype=torch.float16)
+    lse = torch.empty((bh,), device=dev, dtype=torch.float32)
+    assert fa.decode_static_raw(dq, dk, dv, o, lse, None, 1, bh, skv, d, scale, num_splits=4) == fa.FA_OK
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info()
+    for splits in (4, 8, 2):
+        assert fa.decode_static_raw(dq, dk, dv, o, lse, None, 1, bh, skv, d, scale, num_splits=splits) == fa.FA_OK
+    torch.cuda.synchronize()
+    free_after, _ = torch.cuda.mem_get_info()
+    assert free_after == free_before
