@@ -3,8 +3,8 @@
 Tolerances (stated by the task for N(0,1) inputs): fp16 outputs max-abs 2e-3,
 LSE max-abs 1e-3.  bf16 outputs cannot meet 2e-3 against an fp32 oracle because
 rounding a value in [1,2) to bf16 alone moves it by up to 3.9e-3; they are held
-to 1e-2 against the fp32 oracle and to 2 bf16 ulps against the oracle rounded
-to bf16."""
+to 1e-2 against the fp32 oracle and to one bf16 ulp + 3e-3 against the oracle
+rounded to bf16."""
 import ctypes
 
 import numpy as np
@@ -53,10 +53,17 @@ def test_bf16(fa, dev, oracle, d, causal):
     o_ref, l_ref = oracle.attention(q, k, v, scale, causal)
     assert np.abs(lse - l_ref).max() < TOL_LSE
     assert np.abs(o - o_ref).max() < TOL_O_BF16
-    # against the oracle rounded to bf16: 2 output ulps plus the effect of P being
-    # rounded to bf16 before P V (relative 2^-9 per weight, |V| up to ~4)
-    ulp = np.abs(o_ref) * 2.0 ** -7
-    assert (np.abs(o - oracle.round_to(o_ref, "bf16")) <= 2 * ulp + 5e-3).all()
+    # Where the 1e-2 goes: rounding the fp32 result to bf16 alone moves it by up to half an ulp of
+    # bf16 (2^-9 relative: 3.9e-3 for |O| in [1, 2)); the rest is P, which is rounded to bf16 (8
+    # significand bits) before P V.  (P in fp16 next to a bf16 V is not an option: tcgen05.mma
+    # kind::f16 with different A and B formats is an illegal instruction on this GPU.)  The second
+    # bound is against the oracle ROUNDED to bf16: one output ulp for the output rounding itself
+    # plus the measured effect of the bf16 P, printed below.
+    ulp = np.maximum(np.abs(o_ref), 2.0 ** -126) * 2.0 ** -7
+    diff = np.abs(o - oracle.round_to(o_ref, "bf16"))
+    print(f"bf16 d={d} causal={causal}: max|o - o_ref| = {np.abs(o - o_ref).max():.3e}, "
+          f"max(|o - bf16(o_ref)| - ulp) = {(diff - ulp).max():.3e}")
+    assert (diff <= ulp + 3e-3).all()
 
 
 def test_config1_b1_h12_s512_d64_causal(fa, dev, oracle):
