@@ -252,6 +252,7 @@ def run_b200_arm(args, rank, local_rank, world):
         dist.init_process_group("nccl", device_id=dev)
     peaks = load_peaks()
     fa.clear_device_status()
+    fa.set_prefill_variant(args.variant)
 
     B, H, S, D = CFG["B"], CFG["H"], CFG["S"], CFG["D"]
     bh = B * H
@@ -740,6 +741,8 @@ def main():
     ap.add_argument("--gqa-batch", type=int, default=0,
                     help="profiling only: override the batch of the grouped-query decode cases")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--variant", default="auto", choices=["auto", "one_tile", "tile_pair"],
+                    help="profiling only: force one of the two 16-bit prefill kernels")
     args = ap.parse_args()
     if args.batch:
         CFG["B"] = args.batch

@@ -841,8 +841,10 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
 // tile of a head re-reads) inside a share of L2.  Measured on 32 heads of S=8192, d_head 128
 // (134 MB of K and V against 126 MB of L2): walking all heads at once streams K/V from HBM.
 constexpr long long kGroupBytes = FA_GROUP_MB * 1024ll * 1024ll;
+constexpr long long kNoGroupBytes = 64ll * 1024 * 1024;      // half of L2
 int heads_per_group(int n_bh, int seq_len, int d_head, int elem_bytes) {
     const long long per_head = 2ll * seq_len * d_head * elem_bytes;
+    if (per_head * n_bh <= kNoGroupBytes) return n_bh;        // all of K and V fits comfortably: one group
     long long g = kGroupBytes / (per_head > 0 ? per_head : 1);
     if (g < 1) g = 1;
     if (g > n_bh) g = n_bh;
