@@ -219,7 +219,7 @@ def prefill(q, k, v, o, lse, batch_size, num_heads, seq_len, d_head, scale, caus
         raise FaError(rc, "fa_prefill")
 
 
-PREFILL_VARIANTS = {"auto": 0, "one_tile": 1, "tile_pair": 2}
+PREFILL_VARIANTS = {"auto": 0, "one_tile": 1, "tile_pair": 2, "cta_pair": 3}
 
 
 def set_prefill_variant(variant: str) -> None:

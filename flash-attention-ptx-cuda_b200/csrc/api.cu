@@ -214,7 +214,7 @@ FA_EXPORT int fa_prefill_host(const fa_prefill_args* h) {
     if (n_chunks > 16) n_chunks = 16;
     if (n_chunks > bh) n_chunks = bh;
     const size_t heads_per_chunk = (bh + n_chunks - 1) / n_chunks;
-    const int variant = choose_prefill_variant(h->batch_size, h->num_heads, h->seq_len, st);
+    const int variant = choose_prefill_variant(h->batch_size, h->num_heads, h->seq_len, h->d_head, st);
     int ci = 0;
     for (size_t h0 = 0; h0 < bh; h0 += heads_per_chunk, ci++) {
         const size_t nh = (bh - h0 < heads_per_chunk) ? bh - h0 : heads_per_chunk;
@@ -290,7 +290,8 @@ FA_EXPORT const char* fa_error_string(int code) {
 }
 
 FA_EXPORT int fa_set_prefill_variant(int variant) {
-    if (variant != FA_PREFILL_AUTO && variant != FA_PREFILL_ONE_TILE && variant != FA_PREFILL_TILE_PAIR)
+    if (variant != FA_PREFILL_AUTO && variant != FA_PREFILL_ONE_TILE && variant != FA_PREFILL_TILE_PAIR &&
+        variant != FA_PREFILL_CTA_PAIR)
         return FA_ERR_INVALID_ARGUMENT;
     g_prefill_variant.store(variant, std::memory_order_relaxed);
     return FA_OK;

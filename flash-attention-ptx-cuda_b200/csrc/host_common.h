@@ -72,7 +72,9 @@ inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
 // Implemented next to their kernels.
 // `variant` is an FA_PREFILL_* value; FA_PREFILL_AUTO decides from the sizes in `a`.
 int launch_prefill_16bit(const fa_prefill_args& a, DeviceState* st, int variant);
-int choose_prefill_variant(int batch_size, int num_heads, int seq_len, const DeviceState* st);
+int choose_prefill_variant(int batch_size, int num_heads, int seq_len, int d_head, const DeviceState* st);
+// The kernel on pairs of CTAs (d_head 128): builds its own tensor maps (half-tile boxes for K).
+int launch_prefill_2sm_16bit(const fa_prefill_args& a, DeviceState* st, int heads_per_group);
 int launch_prefill_fp8(const fa_prefill_args& a, DeviceState* st);
 // The kernel with two query tiles per CTA (tensor maps as for the one-tile kernel).
 int launch_prefill_pair_16bit(const fa_prefill_args& a, DeviceState* st, const CUtensorMap& tq,

@@ -913,13 +913,10 @@ int launch_gqa_instance(const GqaLaunch& g, DeviceState* st, const CUtensorMap& 
 // spreads a small problem over twice as many SMs and has the shorter critical path.
 std::atomic<int> g_prefill_variant{FA_PREFILL_AUTO};
 
-int choose_prefill_variant(int batch_size, int num_heads, int seq_len, const DeviceState* st) {
+int choose_prefill_variant(int batch_size, int num_heads, int seq_len, int d_head, const DeviceState* st) {
     const int v = g_prefill_variant.load(std::memory_order_relaxed);
     if (v != FA_PREFILL_AUTO) return v;
-    // Measured on B200 (CUDA events, fp16 / bf16, causal and not, S 512 ... 8192): the one-tile kernel
-    // is the faster one on every shape tried so far (0.090 against 0.104 ms on B=8 H=12 S=2048
-    // d_head 64 causal), so it is what the library picks; the tile-pair kernel stays selectable.
-    (void)batch_size; (void)num_heads; (void)seq_len; (void)st;
+    (void)batch_size; (void)num_heads; (void)seq_len; (void)d_head; (void)st;
     return FA_PREFILL_ONE_TILE;
 }
 
@@ -931,7 +928,9 @@ int launch_prefill_16bit(const fa_prefill_args& a, DeviceState* st, int variant)
     if ((rc = make_tensor_map_3d(&tk, a.k, a.dtype, a.d_head, a.seq_len, n_bh, 64, kBN)) != FA_OK) return rc;
     if ((rc = make_tensor_map_3d(&tv, a.v, a.dtype, a.d_head, a.seq_len, n_bh, 64, kBN)) != FA_OK) return rc;
     if ((rc = make_tensor_map_3d(&to, a.o, a.dtype, a.d_head, a.seq_len, n_bh, 64, kBM)) != FA_OK) return rc;
-    if (variant == FA_PREFILL_AUTO) variant = choose_prefill_variant(a.batch_size, a.num_heads, a.seq_len, st);
+    if (variant == FA_PREFILL_AUTO) variant = choose_prefill_variant(a.batch_size, a.num_heads, a.seq_len, a.d_head, st);
+    if (variant == FA_PREFILL_CTA_PAIR && a.d_head == 128)     // built for d_head 128 only; d_head 64 takes the one-tile kernel
+        return launch_prefill_2sm_16bit(a, st, heads_per_group((int)n_bh, a.seq_len, a.d_head, 2));
     if (variant == FA_PREFILL_TILE_PAIR) return launch_prefill_pair_16bit(a, st, tq, tk, tv, to);
     const bool bf = a.dtype == FA_DTYPE_BF16;
     const bool causal = a.causal != 0;

@@ -303,6 +303,100 @@ __device__ __forceinline__ void tmem_st_x16(uint32_t taddr, const uint32_t (&r)[
 }
 
 // ---------------------------------------------------------------------------
+// Two-CTA clusters (tcgen05 cta_group::2): one MMA instruction, issued by a thread of the
+// even ("leader") CTA of a pair, multiplies the 128-row A tiles of BOTH CTAs by a B tile whose
+// N columns are split between the two CTAs' shared memories, accumulating into the same TMEM
+// columns of each CTA.  Every CTA still fetches its own operands; no copy is shared.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Address of the same shared-memory location in CTA `rank` of the cluster (shared::cluster space).
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+    return r;
+}
+// Arrival on a barrier of another CTA of the cluster (address from map_to_cta).
+__device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// try_wait that also orders against arrivals made by the other CTA of the cluster.
+__device__ __forceinline__ bool mbar_try_wait_parked_cluster(uint32_t bar, uint32_t parity, uint32_t hint_ns) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity), "r"(hint_ns)
+        : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, const WaitCtl& ctl,
+                                                  int barrier_id) {
+    const int r = bounded_wait([&] { return mbar_try_wait_parked_cluster(bar, parity, kParkNs); },
+                               [&] { return *ctl.abort_flag != 0; }, [] { return global_timer_ns(); },
+                               kWaitLimitNs, 16u);
+    if (r == kWaitDone) return true;
+    if (r == kWaitTimedOut) {
+        *ctl.abort_flag = 1;
+        atomicCAS(ctl.status, 0, wait_timeout_word(barrier_id));
+    }
+    return false;
+}
+// Whole-warp calls, executed by the same warp index in BOTH CTAs of the pair with the same slot address.
+__device__ __forceinline__ void tmem_alloc_2sm(uint32_t smem_slot, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_slot), "r"(ncols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_2sm(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+// Tiled load into THIS CTA's shared memory whose byte count is credited to the barrier at the same
+// offset in the pair's leader CTA (the thread issuing the pair's MMAs waits there for both halves).
+__device__ __forceinline__ void tma_load_3d_2sm(uint32_t dst, const CUtensorMap* tm, uint32_t bar, int x, int y, int z) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes "
+        "[%0], [%1, {%2, %3, %4}], [%5];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(tm)), "r"(x), "r"(y), "r"(z), "r"(bar & 0xFEFFFFFFu)
+        : "memory");
+}
+// M = 256 over the pair (128 rows per CTA).  Issued by one thread of the leader CTA.
+__device__ __forceinline__ void mma_f16_ss_2sm(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                               uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void mma_f16_ts_2sm(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc,
+                                               uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// Arrives once on the barrier at this offset in BOTH CTAs when every MMA issued so far by this
+// thread has completed.
+__device__ __forceinline__ void tc_commit_2sm(uint32_t bar) {
+    asm volatile(
+        "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+        ::"r"(bar & 0xFEFFFFFFu), "h"(static_cast<uint16_t>(3))
+        : "memory");
+}
+
+// ---------------------------------------------------------------------------
 // Small numeric helpers
 // ---------------------------------------------------------------------------
 __device__ __forceinline__ float ex2_approx(float x) {

@@ -85,7 +85,7 @@ int fa_prefill(const fa_prefill_args* args);
  * kernel on every shape.  This call overrides the choice for the whole process (tests and
  * tuning).  Results are the same within the stated tolerances.
  */
-enum { FA_PREFILL_AUTO = 0, FA_PREFILL_ONE_TILE = 1, FA_PREFILL_TILE_PAIR = 2 };
+enum { FA_PREFILL_AUTO = 0, FA_PREFILL_ONE_TILE = 1, FA_PREFILL_TILE_PAIR = 2, FA_PREFILL_CTA_PAIR = 3 };
 int fa_set_prefill_variant(int variant);
 
 /*

@@ -56,7 +56,7 @@ def golden():
             for name in ("demo_b1h4s256d64", "bench_gate", "normal_small")}
 
 
-@pytest.fixture(params=["auto", "one_tile", "tile_pair"])
+@pytest.fixture(params=["auto", "one_tile", "tile_pair", "cta_pair"])
 def prefill_variant(request, fa):
     """Runs a test once per 16-bit prefill kernel (fa_set_prefill_variant) and once with the
     library's own choice."""

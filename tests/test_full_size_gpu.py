@@ -210,8 +210,8 @@ def test_config2_whole_tensor_every_head_every_row(fa, dev, oracle, prefill_vari
     """B=8 H=12 S=2048 D=64 fp16 causal, the headline configuration: all 96 heads x 2048 rows of O
     and LSE against the CPU oracle on the same rounded inputs, for each of the two kernels."""
     import torch
-    if prefill_variant == "auto":
-        pytest.skip("covered by the explicit variants")
+    if prefill_variant in ("auto", "cta_pair"):
+        pytest.skip("covered by the explicit variants (the CTA-pair kernel is d_head 128 only)")
     bh, s, d = 96, 2048, 64
     q, k, v = (oracle.round_to(x, "f16") for x in oracle.normal_inputs(2002, (bh, s, d)))
     dq, dk, dv = (torch.from_numpy(x).to(dev, torch.float16) for x in (q, k, v))
