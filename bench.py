@@ -46,7 +46,7 @@ PREFILL_TRAFFIC_BYTES = 18.92e6
 PREFILL_TRAFFIC_NOTE = ("ncu on 24 heads: 18.92 MB read (= Q+K+V, 18.87 MB algorithmic), 0 written back during the "
                         "kernel (O and LSE still in L2); scaled by heads")
 DECODE_TRAFFIC_BYTES = 1.0739e9 + 3.9e6   # ncu on B=4 (128 heads): read + write per launch
-CFG = dict(B=8, H=12, S=2048, D=64)
+CFG = dict(B=8, H=12, S=2048, D=64, CAUSAL=True, DTYPE="f16")
 DEC = dict(B=32, H=32, SKV=16384, D=128, SPLITS=16)
 
 
@@ -255,14 +255,16 @@ def run_b200_arm(args, rank, local_rank, world):
     fa.set_prefill_variant(args.variant)
 
     B, H, S, D = CFG["B"], CFG["H"], CFG["S"], CFG["D"]
+    causal, dtype_name = CFG["CAUSAL"], CFG["DTYPE"]
+    tdt = torch.float16 if dtype_name == "f16" else torch.bfloat16
     bh = B * H
-    scale = 0.125
+    scale = float(1.0 / np.sqrt(D))           # 0.125 for the headline workload
     n_sets = 4                                # rotating input sets: 4 x 101 MB > 126 MB of L2
     gen = torch.Generator(device=dev)
     gen.manual_seed(2002 + rank)
     sets = []
     for _ in range(n_sets):
-        q, k, v = (torch.randn((bh, S, D), device=dev, dtype=torch.float32, generator=gen).to(torch.float16)
+        q, k, v = (torch.randn((bh, S, D), device=dev, dtype=torch.float32, generator=gen).to(tdt)
                    for _ in range(3))
         o = torch.empty_like(q)
         lse = torch.empty((bh, S), device=dev, dtype=torch.float32)
@@ -278,8 +280,9 @@ def run_b200_arm(args, rank, local_rank, world):
         out = []
         for (q, k, v, o, lse) in sets:
             out.append(fa.PrefillArgs(q[head0:].data_ptr(), k[head0:].data_ptr(), v[head0:].data_ptr(),
-                                      o[head0:].data_ptr(), lse[head0:].data_ptr(), 1, n_heads, S, D, scale, 1,
-                                      fa.FA_DTYPE_F16, None, None, None, stream.cuda_stream or None))
+                                      o[head0:].data_ptr(), lse[head0:].data_ptr(), 1, n_heads, S, D, scale,
+                                      int(causal), fa.DTYPES[dtype_name], None, None, None,
+                                      stream.cuda_stream or None))
         return out
 
     full_args = launch_args(bh, 0)
@@ -317,7 +320,7 @@ def run_b200_arm(args, rank, local_rank, world):
 
     sampler = ClockSampler(physical_index(local_rank))
     warmup = max(args.warmup, 3)
-    flops_step = causal_flops(bh, S, D)
+    flops_step = causal_flops(bh, S, D) if causal else refconv_flops(bh, S, D)
     # One timed loop of K steps of this workload lasts a few milliseconds, too short for a clock
     # record or a steady number.  The loop (exactly K steps between two barriers, max over ranks) is
     # therefore repeated until about 60 ms have been timed; the headline is the MEDIAN repeat, every
@@ -434,6 +437,16 @@ def run_b200_arm(args, rank, local_rank, world):
             "clocks": clocks,
             "device_status": status,
         }
+        if args.shape:
+            # a profiling shape, not the headline workload: say so in every label a reader sees
+            what = (f"{'causal' if causal else 'non-causal'} prefill {dtype_name} B={B} H={H} S={S} D={D} "
+                    f"(--shape, not the headline workload)")
+            line["metric"] = what
+            line["unit"] = line["e2e"]["unit"] = "TFLOP/s (causal FLOP count)" if causal else "TFLOP/s"
+            line["dtype"] = dtype_name
+            line["config"]["workload"] = what
+            line["roofline"].update(kernel=f"16-bit prefill kernel, variant {args.variant}", traffic=None,
+                                    traffic_note="not captured for this shape")
         if strong:
             line["strong_scaling_96_heads"] = strong
         if kv_sharded:
@@ -741,11 +754,17 @@ def main():
     ap.add_argument("--gqa-batch", type=int, default=0,
                     help="profiling only: override the batch of the grouped-query decode cases")
     ap.add_argument("--no-cpu", action="store_true")
-    ap.add_argument("--variant", default="auto", choices=["auto", "one_tile", "tile_pair"],
-                    help="profiling only: force one of the two 16-bit prefill kernels")
+    ap.add_argument("--variant", default="auto", choices=["auto", "one_tile", "tile_pair", "cta_pair"],
+                    help="profiling only: force one of the 16-bit prefill kernels")
+    ap.add_argument("--shape", default="",
+                    help="profiling only: B,H,S,D,causal(0/1),dtype(f16/bf16) instead of the headline workload "
+                         "(the line is then not the headline)")
     args = ap.parse_args()
     if args.batch:
         CFG["B"] = args.batch
+    if args.shape:
+        b, h, sq, d, c, dt = args.shape.split(",")
+        CFG.update(B=int(b), H=int(h), S=int(sq), D=int(d), CAUSAL=bool(int(c)), DTYPE=dt)
     if args.decode_batch:
         DEC["B"] = args.decode_batch
     rank = int(os.environ.get("RANK", "0"))

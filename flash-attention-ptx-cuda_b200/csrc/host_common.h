@@ -77,7 +77,7 @@ int choose_prefill_variant(int batch_size, int num_heads, int seq_len, int d_hea
 int launch_prefill_2sm_16bit(const fa_prefill_args& a, DeviceState* st, int heads_per_group);
 int launch_prefill_fp8(const fa_prefill_args& a, DeviceState* st);
 // The kernel with two query tiles per CTA (tensor maps as for the one-tile kernel).
-int launch_prefill_pair_16bit(const fa_prefill_args& a, DeviceState* st, const CUtensorMap& tq,
+int launch_prefill_pair_16bit(const fa_prefill_args& a, DeviceState* st, int heads_per_group, const CUtensorMap& tq,
                               const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& to);
 // FA_PREFILL_* choice made through fa_set_prefill_variant().
 extern std::atomic<int> g_prefill_variant;

@@ -931,7 +931,7 @@ int launch_prefill_16bit(const fa_prefill_args& a, DeviceState* st, int variant)
     if (variant == FA_PREFILL_AUTO) variant = choose_prefill_variant(a.batch_size, a.num_heads, a.seq_len, a.d_head, st);
     if (variant == FA_PREFILL_CTA_PAIR && a.d_head == 128)     // built for d_head 128 only; d_head 64 takes the one-tile kernel
         return launch_prefill_2sm_16bit(a, st, heads_per_group((int)n_bh, a.seq_len, a.d_head, 2));
-    if (variant == FA_PREFILL_TILE_PAIR) return launch_prefill_pair_16bit(a, st, tq, tk, tv, to);
+    if (variant == FA_PREFILL_TILE_PAIR) return launch_prefill_pair_16bit(a, st, heads_per_group((int)n_bh, a.seq_len, a.d_head, 2), tq, tk, tv, to);
     const bool bf = a.dtype == FA_DTYPE_BF16;
     const bool causal = a.causal != 0;
 #define FA_DISPATCH(DH)                                                                      \

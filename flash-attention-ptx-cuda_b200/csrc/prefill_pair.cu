@@ -158,12 +158,18 @@ struct PairItem {
 
 template <bool CAUSAL>
 __device__ __forceinline__ bool get_pair_item(int round, int n_items, int n_bh, int n_pairs, int seq_len,
-                                              PairItem& it) {
+                                              int heads_per_group, PairItem& it) {
     const int G = gridDim.x, c = blockIdx.x;
     const int idx = (round & 1) ? round * G + (G - 1 - c) : round * G + c;
     if (idx >= n_items) return false;
-    const int pr = CAUSAL ? (n_pairs - 1 - idx / n_bh) : idx / n_bh;
-    it.bh = idx % n_bh;
+    // Heads are walked in groups whose K/V fit in L2 together (one group = all heads when the
+    // whole problem fits); inside a group the order is (pair, head) as before.
+    const int per_group = heads_per_group * n_pairs;
+    const int gi = idx / per_group, rem = idx - gi * per_group;
+    const int h0 = gi * heads_per_group, hin = min(heads_per_group, n_bh - h0);
+    const int rank = rem / hin;
+    const int pr = CAUSAL ? (n_pairs - 1 - rank) : rank;
+    it.bh = h0 + rem - rank * hin;
     it.qa = pr * 2 * kBM;
     const int n_all = (seq_len + kBN - 1) / kBN;
     const bool has_b = it.qa + kBM < seq_len;
@@ -178,7 +184,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 prefill_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                     const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o,
                     float* __restrict__ lse_out, int seq_len, int n_bh, int n_pairs, int n_items,
-                    float scale_log2, int* status) {
+                    int heads_per_group, float scale_log2, int* status) {
     using L = PairSmem<D>;
     constexpr int NBOX = L::kNBox, NK = L::NK, NV = L::NV, NO = L::NO;
     constexpr bool INPLACE = (D == 128);                  // P overwrites the scores it came from
@@ -259,7 +265,7 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
             bool ok = true;
             for (int r = 0; ok && r < n_rounds; r++) {
                 PairItem it;
-                if (!get_pair_item<CAUSAL>(r, n_items, n_bh, n_pairs, seq_len, it)) continue;
+                if (!get_pair_item<CAUSAL>(r, n_items, n_bh, n_pairs, seq_len, heads_per_group, it)) continue;
                 for (int j = 0; j < it.n; j++, g++) {
                     const int ua = j < it.n_a ? t_a + j : -1, ub = j < it.n_b ? t_b + j : -1;
                     if (do_k) {
@@ -362,7 +368,7 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         bool ok = true;
         for (int r = 0; ok && r < n_rounds; r++) {
             PairItem it;
-            if (!get_pair_item<CAUSAL>(r, n_items, n_bh, n_pairs, seq_len, it)) continue;
+            if (!get_pair_item<CAUSAL>(r, n_items, n_bh, n_pairs, seq_len, heads_per_group, it)) continue;
             const int X = warp == kWarpChainA ? 0 : 1;
             const int n_x = X ? it.n_b : it.n_a;
             if (n_x > 0) {
@@ -404,7 +410,7 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         bool ok = true;
         for (int r = 0; ok && r < n_rounds; r++) {
             PairItem it;
-            if (!get_pair_item<CAUSAL>(r, n_items, n_bh, n_pairs, seq_len, it)) continue;
+            if (!get_pair_item<CAUSAL>(r, n_items, n_bh, n_pairs, seq_len, heads_per_group, it)) continue;
 #pragma unroll
             for (int X = 0; X < 2; X++) {
                 const int n_x = X ? it.n_b : it.n_a;
@@ -478,7 +484,7 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
 
         for (int r = 0; ok && r < n_rounds; r++) {
             PairItem it;
-            if (!get_pair_item<CAUSAL>(r, n_items, n_bh, n_pairs, seq_len, it)) continue;
+            if (!get_pair_item<CAUSAL>(r, n_items, n_bh, n_pairs, seq_len, heads_per_group, it)) continue;
             const int n_x = X ? it.n_b : it.n_a;
             if (n_x == 0) continue;
             const int q_start = it.qa + X * kBM;
@@ -625,8 +631,8 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
 }
 
 template <int D, bool CAUSAL, bool BF16>
-int launch_pair_instance(const fa_prefill_args& a, DeviceState* st, const CUtensorMap& tq, const CUtensorMap& tk,
-                         const CUtensorMap& tv, const CUtensorMap& to) {
+int launch_pair_instance(const fa_prefill_args& a, DeviceState* st, int heads_per_group, const CUtensorMap& tq,
+                         const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& to) {
     using L = PairSmem<D>;
     auto kernel = prefill_pair_kernel<D, CAUSAL, BF16>;
     static bool configured[64] = {};
@@ -641,22 +647,22 @@ int launch_pair_instance(const fa_prefill_args& a, DeviceState* st, const CUtens
     if (n_items > 0x7FFFFFFFll) return FA_ERR_INVALID_ARGUMENT;
     const unsigned grid = (unsigned)(n_items < st->sm_count ? n_items : st->sm_count);
     kernel<<<grid, kThreads, L::kTotal, static_cast<cudaStream_t>(a.stream)>>>(
-        tq, tk, tv, to, a.lse, a.seq_len, n_bh, n_pairs, (int)n_items, a.scale * kLog2e, st->status);
+        tq, tk, tv, to, a.lse, a.seq_len, n_bh, n_pairs, (int)n_items, heads_per_group, a.scale * kLog2e, st->status);
     FA_CUDA_TRY(cudaGetLastError());
     return FA_OK;
 }
 
 }  // namespace
 
-int launch_prefill_pair_16bit(const fa_prefill_args& a, DeviceState* st, const CUtensorMap& tq,
+int launch_prefill_pair_16bit(const fa_prefill_args& a, DeviceState* st, int heads_per_group, const CUtensorMap& tq,
                               const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& to) {
     const bool bf = a.dtype == FA_DTYPE_BF16;
     const bool causal = a.causal != 0;
-#define FA_DISPATCH(DH)                                                                   \
-    (causal ? (bf ? launch_pair_instance<DH, true, true>(a, st, tq, tk, tv, to)           \
-                  : launch_pair_instance<DH, true, false>(a, st, tq, tk, tv, to))         \
-            : (bf ? launch_pair_instance<DH, false, true>(a, st, tq, tk, tv, to)          \
-                  : launch_pair_instance<DH, false, false>(a, st, tq, tk, tv, to)))
+#define FA_DISPATCH(DH)                                                                               \
+    (causal ? (bf ? launch_pair_instance<DH, true, true>(a, st, heads_per_group, tq, tk, tv, to)      \
+                  : launch_pair_instance<DH, true, false>(a, st, heads_per_group, tq, tk, tv, to))    \
+            : (bf ? launch_pair_instance<DH, false, true>(a, st, heads_per_group, tq, tk, tv, to)     \
+                  : launch_pair_instance<DH, false, false>(a, st, heads_per_group, tq, tk, tv, to)))
     if (a.d_head == 64) return FA_DISPATCH(64);
     return FA_DISPATCH(128);
 #undef FA_DISPATCH
