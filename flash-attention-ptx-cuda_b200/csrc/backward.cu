@@ -16,26 +16,35 @@
 //                         memory, the query tiles stream past; per step
 //                         S^T = K Q^T and dP^T = V dO^T on the tensor core (so a
 //                         thread owns a KEY row in TMEM), P^T and dS^T are written back
-//                         to TMEM as 16-bit in place, then dV += P^T dO and dK += dS^T Q
-//                         with those as the TMEM operand.
+//                         to TMEM as 16-bit, then dV += P^T dO and dK += dS^T Q with
+//                         those as the TMEM operand.
 //   bwd_kernel<MODE 1>    one CTA per (query tile, head): Q and dO stay, the key tiles
-//                         stream; S = Q K^T, dP = dO V^T, dS in place, dQ += dS K.
+//                         stream; S = Q K^T, dP = dO V^T, dS to TMEM, dQ += dS K.
 //                         (S and dP are computed twice overall; nothing is accumulated
 //                         across CTAs.)
 // Both modes are the same code: two stationary tiles A0, A1, two streamed tiles B0,
 // B1 per step, products T0 = A0 B0^T and T1 = A1 B1^T, accumulators fed from TMEM.
-// A step streams 64 rows; the products alternate between two TMEM buffers, so the
-// threads work on step t+1 while the accumulating MMAs of step t run.
-//   warps 0-7  two threads per stationary row (TMEM lane): warps 0-3 take the first 32
-//              streamed columns of a step, warps 4-7 the other 32: exponentials, dS,
-//              16-bit write-back (each half into the columns it has read itself), final
-//              conversion and store of the accumulators.
-//   warp 8     lane 0 issues the TMA loads and the product MMAs; the products of step
-//              t+2 are issued once the accumulations of step t, which read the same
-//              TMEM buffer, have completed.
-//   warp 9     lane 0 issues the accumulating MMAs of a step as soon as its 16-bit
-//              operands are in TMEM (an MMA costs its issuing thread 50-100 clocks, so
-//              the two streams have an issuer each, as in the forward kernel).
+// A step streams 64 rows.  Even steps use one TMEM product buffer, odd steps the other, and
+// each parity has its own compute warps and its own product issuer, so the two chains
+//     products(t) -> exponentials, dS -> accumulating MMAs(t)
+// run a step apart and fill each other's waits.  The 16-bit operands of the accumulating
+// MMAs get TMEM columns of their own, so a product buffer is free again as soon as its
+// values are in registers (d_head 128, MODE 0 has no columns left for that: there the
+// operands overwrite the products and the buffer is free when the accumulations are done).
+//   warps 0-7    even steps, two threads per stationary row (TMEM lane): warps 0-3 take the
+//                first 32 streamed columns of a step, warps 4-7 the other 32: exponentials,
+//                dS, 16-bit operands to TMEM; at the end conversion and store of the
+//                accumulators.
+//   warps 8-15   the same for odd steps.
+//   warps 16, 17 lane 0 issues the product MMAs of even / odd steps.
+//   warps 18, 19 lane 0 issues the accumulating MMAs, one accumulator each (dV and dK; the
+//                dQ kernel uses warp 18 only), every step in order.
+//   warp 20      lane 0 issues the TMA loads of the streamed tiles.
+// An MMA costs its issuing thread 55-110 clocks whatever its size, and two threads issue twice
+// as many (measured), so every MMA stream has a thread of its own; and the per-step waits of
+// a compute warp (products ready, operand columns free, stores complete) are latencies that
+// only other warps' work can fill, hence sixteen compute warps on two steps rather than
+// eight on one.
 #include <cmath>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
@@ -47,15 +56,22 @@
 namespace fa {
 namespace {
 
-constexpr int kT = 128;                  // tile edge: stationary rows per CTA, streamed rows per step
-constexpr int kBwdThreads = 320;
-constexpr int kCtlWarp = 8;          // TMA loads and the product MMAs
-constexpr int kAccWarp = 9;          // the accumulating MMAs
+constexpr int kT = 128;                  // tile edge: stationary rows per CTA
+constexpr int kBwdThreads = 768;         // 24 warps (21-23 idle: register pools move by groups of four warps)
+constexpr int kComputeWarps = 16;
+constexpr int kProdWarp = 16;            // 16, 17: product MMAs of even / odd steps
+constexpr int kAccWarp = 18;             // 18, 19: accumulating MMAs, one accumulator each
+constexpr int kLoadWarp = 20;            // TMA loads of the streamed tiles
 constexpr int kW = 64;                   // streamed rows per step (columns of one product)
-constexpr int kStages = 4;               // streamed (B0, B1) tile pairs in flight
 constexpr float kLog2e = 1.4426950408889634f;
+// setmaxnreg moves registers inside the pool the CTA got at launch (threads x registers at launch)
+constexpr int kBwdRegsLaunch = (65536 / kBwdThreads) / 8 * 8;
+constexpr int kBwdRegsCompute = 104;     // warps 0-15
+constexpr int kBwdRegsRest = 32;         // warps 16-23
+static_assert(512 * kBwdRegsCompute + 256 * kBwdRegsRest <= kBwdThreads * kBwdRegsLaunch,
+              "setmaxnreg targets exceed the CTA's register pool");
 
-enum : int { kBwdBarA = 21, kBwdBarFull = 22, kBwdBarT = 23, kBwdBarP = 24, kBwdBarFree = 25, kBwdBarDone = 26, kBwdBarStep = 27 };
+enum : int { kBwdBarA = 21, kBwdBarFull = 22, kBwdBarT = 23, kBwdBarP = 24, kBwdBarFree = 25, kBwdBarDone = 26, kBwdBarAcc = 27 };
 
 template <int D>
 struct BwdSmem {
@@ -64,13 +80,19 @@ struct BwdSmem {
     static constexpr int kTile = kNBox * kBox;        // one 128 x D 16-bit tile (stationary operands)
     static constexpr int kBoxB = kW * 128;            // one box of a streamed tile: kW rows x 128 bytes
     static constexpr int kTileB = kNBox * kBoxB;      // one kW x D streamed tile
+    // streamed (B0, B1) tile pairs in flight: a pair is requested when the accumulations of the
+    // step that held its stage have completed, and a load takes longer than a step
+    static constexpr int kStages = (D == 64) ? 8 : 4;
     static constexpr int kTotal = 2 * kTile + kStages * 2 * kTileB + 1024;
 };
 
-// TMEM column (relative to T0 / T1) of the 16-bit operand slice for streamed rows [16 kk, 16 kk + 16)
-// of a step: each half of the compute warps writes its 16 columns of pairs over the start of the 32
-// fp32 columns it reads, so the slices of streamed rows 32-63 start at column 32.
-__host__ __device__ constexpr uint32_t op16_col(int kk) { return (kk < 2 ? 0u : 32u) + (kk & 1) * 8u; }
+// TMEM column, relative to the operand's first, of the 16-bit slice for streamed rows
+// [16 kk, 16 kk + 16) of a step.  Each half of a parity's compute warps writes 16 columns of pairs:
+// side by side where the operands have columns of their own; in place each half writes over the
+// start of the 32 fp32 columns it has read, so the slices of streamed rows 32-63 start at column 32.
+__host__ __device__ constexpr uint32_t op16_col(int kk, bool in_place) {
+    return in_place ? (kk < 2 ? 0u : 32u) + (kk & 1) * 8u : kk * 8u;
+}
 
 template <bool BF16>
 __global__ void delta_kernel(const uint16_t* __restrict__ o, const uint16_t* __restrict__ d_o,
@@ -108,19 +130,25 @@ bwd_kernel(const __grid_constant__ CUtensorMap ta0, const __grid_constant__ CUte
            const float* __restrict__ lse, const float* __restrict__ delta, uint16_t* __restrict__ out0,
            uint16_t* __restrict__ out1, int seq_len, int n_tiles, float scale, int* status) {
     using L = BwdSmem<D>;
-    constexpr int NBOX = L::kNBox;
+    constexpr int NBOX = L::kNBox, kStages = L::kStages;
     constexpr uint32_t FMT = BF16 ? kFmtBF16 : kFmtF16;
-    // TMEM: two product buffers of 128 columns (T0 in the first kW, T1 in the second kW), then the
-    // accumulators
+    constexpr int NACC = (MODE == 0) ? 2 : 1;             // accumulators = accumulation issuers
+    // TMEM: two product buffers of 128 columns (T0 in the first kW, T1 in the second kW), the
+    // accumulators, then the 16-bit operands of each parity (P^T in 32 columns, dS in the next 32).
+    // d_head 128, MODE 0: the accumulators take what is left, the operands overwrite the start of
+    // T0 / T1.
+    constexpr bool INPLACE = (MODE == 0 && D == 128);
     constexpr uint32_t ACC0_COL = 256, ACC1_COL = 256 + D;
-    static_assert(ACC1_COL + D <= 512, "TMEM columns");
+    constexpr uint32_t OP_COL = 256 + NACC * D;
+    static_assert(ACC1_COL + (MODE == 0 ? D : 0) <= 512 && (INPLACE || OP_COL + 128 <= 512), "TMEM columns");
+    constexpr uint32_t OPP0 = INPLACE ? 0u : OP_COL, OPD0 = INPLACE ? (uint32_t)kW : OP_COL + 32;   // parity 0
+    constexpr uint32_t OP_STRIDE = INPLACE ? 128u : 64u;                                             // to parity 1
 
     extern __shared__ uint8_t smem_raw[];
-    __shared__ __align__(8) uint64_t bar_a, bar_full[kStages], bar_acc[kStages], bar_t[2], bar_p[2], bar_done;
-    __shared__ __align__(8) uint64_t bar_step;            // MODE 0: rendezvous of the compute warps, once per step
-    // MODE 0: statistics of the streamed queries by step parity, per column pair
+    __shared__ __align__(8) uint64_t bar_a, bar_full[kStages], bar_acc[kStages], bar_t[2], bar_tfree[2], bar_p[2], bar_done;
+    // MODE 0: statistics of the streamed queries of a group's current / next step, per column pair
     // {-lse*log2e (col 0, col 1), -delta*scale (col 0, col 1)}: the addends of the two packed FMAs
-    __shared__ __align__(16) float st_neg[2][kW / 2][4];
+    __shared__ __align__(16) float st_neg[2][2][kW / 2][4];
     __shared__ uint32_t tmem_slot;
     __shared__ int abort_flag;
 
@@ -140,13 +168,13 @@ bwd_kernel(const __grid_constant__ CUtensorMap ta0, const __grid_constant__ CUte
     if (MODE == 0 && tid == 0) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     if (tid == 0) {
         mbar_init(smem_u32(&bar_a), 1);
-        for (int i = 0; i < kStages; i++) { mbar_init(smem_u32(&bar_full[i]), 1); mbar_init(smem_u32(&bar_acc[i]), 1); }
+        for (int i = 0; i < kStages; i++) { mbar_init(smem_u32(&bar_full[i]), 1); mbar_init(smem_u32(&bar_acc[i]), NACC); }
         for (int i = 0; i < 2; i++) {
             mbar_init(smem_u32(&bar_t[i]), 1);
-            mbar_init(smem_u32(&bar_p[i]), 8);           // one arrival per compute warp
+            mbar_init(smem_u32(&bar_tfree[i]), 8);       // one arrival per compute warp of the parity
+            mbar_init(smem_u32(&bar_p[i]), 8);
         }
-        mbar_init(smem_u32(&bar_done), 1);
-        mbar_init(smem_u32(&bar_step), 8);
+        mbar_init(smem_u32(&bar_done), NACC);
         abort_flag = 0;
         fence_mbar_init();
     }
@@ -161,7 +189,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap ta0, const __grid_constant__ CUte
             tma_load_3d(dst + L::kTileB + b * L::kBoxB, &tb1, smem_u32(&bar_full[s]), b * 64, row0 + t * kW, bh);
         }
     };
-    if (warp == kCtlWarp) {
+    if (warp == kLoadWarp) {
         // the first loads go out before the TMEM allocation, so their latency overlaps it
         if (lane == 0) {
             mbar_arrive_expect_tx(smem_u32(&bar_a), 2 * L::kTile);
@@ -178,19 +206,37 @@ bwd_kernel(const __grid_constant__ CUtensorMap ta0, const __grid_constant__ CUte
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = tmem_slot;
+    if (warp >= kComputeWarps) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kBwdRegsRest));
 
-    if (warp == kCtlWarp) {
-        // ------------------------------------------------------------ TMA + MMA issue (one thread)
+    if (warp == kLoadWarp) {
+        // ------------------------------------------------------------ TMA loads (one thread)
         if (lane == 0) {
+            for (int u = kStages; u < n_steps; u++) {
+                // stage u % kStages held step u - kStages: its accumulations must have completed
+                if (!mbar_wait(smem_u32(&bar_acc[u % kStages]), ((u - kStages) / kStages) & 1, ctl, kBwdBarFree)) break;
+                load_step(u);
+            }
+        }
+        __syncwarp();
+    } else if (warp == kProdWarp || warp == kProdWarp + 1) {
+        // ------------------------------------------------------------ product MMAs of one parity (one thread)
+        if (lane == 0) {
+            const int g = warp - kProdWarp;
             constexpr uint32_t idesc_t = make_idesc(kT, kW, FMT, FMT, kMajorK, kMajorK);
             constexpr uint64_t hi_k = make_sdesc_hi(16, 1024);
-
-            // products of step t into buffer t & 1: T0 = A0 B0^T, T1 = A1 B1^T (kW columns each)
-            auto issue_products = [&](int t) -> bool {
+            const uint32_t tb = tmem + g * 128;
+            bool ok = mbar_wait(smem_u32(&bar_a), 0, ctl, kBwdBarA);
+            for (int t = g; ok && t < n_steps; t += 2) {
                 const int s = t % kStages;
                 const uint32_t b0_s = b_s + s * 2 * L::kTileB, b1_s = b0_s + L::kTileB;
-                const uint32_t tb = tmem + (t & 1) * 128;
-                if (!mbar_wait(smem_u32(&bar_full[s]), (t / kStages) & 1, ctl, kBwdBarFull)) return false;
+                // the tiles arrived long ago; the buffer is what the issue waits for
+                if (!mbar_wait(smem_u32(&bar_full[s]), (t / kStages) & 1, ctl, kBwdBarFull)) break;
+                if (t >= 2) {
+                    // products of step t reuse the TMEM buffer of step t-2
+                    if (INPLACE) ok = mbar_wait(smem_u32(&bar_acc[(t - 2) % kStages]), ((t - 2) / kStages) & 1, ctl, kBwdBarAcc);
+                    else         ok = mbar_wait(smem_u32(&bar_tfree[g]), ((t >> 1) - 1) & 1, ctl, kBwdBarFree);
+                    if (!ok) break;
+                }
                 tc_fence_after();
 #pragma unroll
                 for (int kk = 0; kk < D / 16; kk++) {
@@ -202,58 +248,42 @@ bwd_kernel(const __grid_constant__ CUtensorMap ta0, const __grid_constant__ CUte
                     const uint32_t offa = (kk >> 2) * L::kBox + (kk & 3) * 32, offb = (kk >> 2) * L::kBoxB + (kk & 3) * 32;
                     mma_f16_ss(tb + kW, make_sdesc(a1_s + offa, hi_k), make_sdesc(b1_s + offb, hi_k), idesc_t, kk > 0);
                 }
-                tc_commit(smem_u32(&bar_t[t & 1]));
-                return true;
-            };
-            bool ok = mbar_wait(smem_u32(&bar_a), 0, ctl, kBwdBarA);
-            for (int t = 0; ok && t < n_steps; t++) {
-                if (t >= 2) {
-                    // the products of step t reuse the TMEM buffer of step t-2, and step t-2+kStages its
-                    // shared-memory stage: the accumulations of step t-2 must have completed
-                    if (!mbar_wait(smem_u32(&bar_acc[(t - 2) % kStages]), ((t - 2) / kStages) & 1, ctl, kBwdBarFree)) break;
-                    if (t - 2 + kStages < n_steps) load_step(t - 2 + kStages);
-                }
-                ok = issue_products(t);
+                tc_commit(smem_u32(&bar_t[g]));
             }
         }
         __syncwarp();
-    } else if (warp == kAccWarp) {
-        // ------------------------------------------------------------ accumulating MMAs (one thread)
+    } else if (warp == kAccWarp || (warp == kAccWarp + 1 && MODE == 0)) {
+        // ------------------------------------------------------------ accumulating MMAs of one accumulator (one thread)
         if (lane == 0) {
+            const int x = warp - kAccWarp;
             constexpr uint32_t idesc_acc = make_idesc(kT, D, FMT, FMT, kMajorK, kMajorMN);
             constexpr uint64_t hi_mn = make_sdesc_hi(L::kBoxB, 1024);
+            // MODE 0: warp 10 dV += P^T dO (operand P^T, streamed dO = B1), warp 11 dK += dS^T Q (dS^T, Q = B0)
+            // MODE 1: warp 10 dQ += dS K (dS, K = B0)
+            const bool use_p = (MODE == 0 && x == 0);
+            const uint32_t acc = tmem + (x == 0 ? ACC0_COL : ACC1_COL);
+            const uint32_t op0 = tmem + (use_p ? OPP0 : OPD0);
             for (int t = 0; t < n_steps; t++) {
-                const int s = t % kStages;
-                const uint32_t b0_s = b_s + s * 2 * L::kTileB, b1_s = b0_s + L::kTileB;
-                const uint32_t tb = tmem + (t & 1) * 128;
-                if (!mbar_wait(smem_u32(&bar_p[t & 1]), (t >> 1) & 1, ctl, kBwdBarP)) break;
+                const int s = t % kStages, g = t & 1;
+                const uint32_t bt_s = b_s + s * 2 * L::kTileB + (use_p ? L::kTileB : 0);
+                if (!mbar_wait(smem_u32(&bar_p[g]), (t >> 1) & 1, ctl, kBwdBarP)) break;
                 tc_fence_after();
-                if (MODE == 0) {
-                    // dV += P^T dO (P^T over T0), dK += dS^T Q (dS^T over T1)
 #pragma unroll
-                    for (int kk = 0; kk < kW / 16; kk++)
-                        mma_f16_ts(tmem + ACC0_COL, tb + op16_col(kk), make_sdesc(b1_s + kk * 2048, hi_mn),
-                                   idesc_acc, (t > 0 || kk > 0) ? 1u : 0u);
-#pragma unroll
-                    for (int kk = 0; kk < kW / 16; kk++)
-                        mma_f16_ts(tmem + ACC1_COL, tb + kW + op16_col(kk), make_sdesc(b0_s + kk * 2048, hi_mn),
-                                   idesc_acc, (t > 0 || kk > 0) ? 1u : 0u);
-                } else {
-                    // dQ += dS K
-#pragma unroll
-                    for (int kk = 0; kk < kW / 16; kk++)
-                        mma_f16_ts(tmem + ACC0_COL, tb + kW + op16_col(kk), make_sdesc(b0_s + kk * 2048, hi_mn),
-                                   idesc_acc, (t > 0 || kk > 0) ? 1u : 0u);
-                }
+                for (int kk = 0; kk < kW / 16; kk++)
+                    mma_f16_ts(acc, op0 + g * OP_STRIDE + op16_col(kk, INPLACE), make_sdesc(bt_s + kk * 2048, hi_mn), idesc_acc,
+                               (t > 0 || kk > 0) ? 1u : 0u);
                 tc_commit(smem_u32(&bar_acc[s]));
                 if (t == n_steps - 1) tc_commit(smem_u32(&bar_done));
             }
         }
         __syncwarp();
-    } else {
-        // ------------------------------------------------------------ two threads per stationary row
-        const int r = tid & (kT - 1);                       // == TMEM lane: (warp & 3) * 32 + lane
-        const int half = warp >> 2;                         // which 32 streamed columns of a step
+    } else if (warp < kComputeWarps) {
+        // ------------------------------------------------------------ two threads per stationary row and parity
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kBwdRegsCompute));
+        const int g = warp >> 3;                            // parity of the steps this warp works on
+        const int half = (warp >> 2) & 1;                   // which 32 streamed columns of a step
+        const int gt = tid & 255;                           // thread within the parity's two groups
+        const int r = tid & (kT - 1);                       // == TMEM lane
         const int r_glob = tile * kT + r;
         const uint32_t lane_off = static_cast<uint32_t>((warp & 3) * 32) << 16;
         const float scale_log2 = scale * kLog2e;
@@ -262,94 +292,112 @@ bwd_kernel(const __grid_constant__ CUtensorMap ta0, const __grid_constant__ CUte
         // MODE 1: the statistics belong to this thread's query row.  +inf as LSE makes p = 0.
         float row_lse2 = INFINITY, row_delta = 0.0f;
         if (MODE == 1 && r_glob < seq_len) { row_lse2 = lse_h[r_glob] * kLog2e; row_delta = delta_h[r_glob]; }
-        // MODE 0: statistics of the streamed queries, one per column, staged in shared memory one step
-        // ahead by threads 0..kW-1 and fetched from global memory two steps ahead; rows past the end
-        // get LSE = +inf (p = 0)
+        // MODE 0: statistics of the streamed queries, one per column: threads 0..kW-1 of the parity
+        // fetch those of its step after next from global memory and stage those of its next step in
+        // shared memory while the current ones are in use; rows past the end get LSE = +inf
         auto fetch_stats = [&](int t, float& l2, float& dl) {
-            const int qi = row0 + t * kW + tid;
+            const int qi = row0 + t * kW + gt;
             l2 = INFINITY;
             dl = 0.0f;
-            if (MODE == 0 && tid < kW && t < n_steps && qi < seq_len) { l2 = lse_h[qi] * kLog2e; dl = delta_h[qi]; }
+            if (MODE == 0 && gt < kW && t < n_steps && qi < seq_len) { l2 = lse_h[qi] * kLog2e; dl = delta_h[qi]; }
+        };
+        auto stage_stats = [&](int slot, float l2, float dl) {
+            if (gt < kW) { st_neg[g][slot][gt >> 1][gt & 1] = -l2; st_neg[g][slot][gt >> 1][2 + (gt & 1)] = -dl * scale; }
         };
         float nx_l2, nx_dl;
         if (MODE == 0) {
-            fetch_stats(0, nx_l2, nx_dl);
-            if (tid < kW) { st_neg[0][tid >> 1][tid & 1] = -nx_l2; st_neg[0][tid >> 1][2 + (tid & 1)] = -nx_dl * scale; }
-            fetch_stats(1, nx_l2, nx_dl);
+            fetch_stats(g, nx_l2, nx_dl);
+            stage_stats(0, nx_l2, nx_dl);
+            fetch_stats(g + 2, nx_l2, nx_dl);
         }
+        const uint64_t scale_log2_2 = pack2(scale_log2, scale_log2), scale2 = pack2(scale, scale);
+        const uint64_t row_neg_l2 = pack2(-row_lse2, -row_lse2), row_neg_dl = pack2(-row_delta * scale, -row_delta * scale);
         bool ok = true;
-        for (int t = 0; ok && t < n_steps; t++) {
+        for (int t = g; t < n_steps; t += 2) {
+            const int i = t >> 1;
             const int c0 = row0 + t * kW;                   // first streamed row (= column of T0/T1) of the step
-            const uint32_t tb = tmem + lane_off + (t & 1) * 128;
+            const uint32_t tb = tmem + lane_off + g * 128 + half * 32;
+            ok = ok && __all_sync(0xffffffffu, mbar_wait(smem_u32(&bar_t[g]), i & 1, ctl, kBwdBarT));
             if (MODE == 0) {
-                // step t-1's readers are past their reads of the other parity; this step's values
-                // (written a step ago) become visible
-                __syncwarp();
-                if (lane == 0) mbar_arrive(smem_u32(&bar_step));
-                if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&bar_step), t & 1, ctl, kBwdBarStep))) { ok = false; break; }
-                if (tid < kW) {
-                    st_neg[(t + 1) & 1][tid >> 1][tid & 1] = -nx_l2;
-                    st_neg[(t + 1) & 1][tid >> 1][2 + (tid & 1)] = -nx_dl * scale;
-                }
-                fetch_stats(t + 2, nx_l2, nx_dl);
+                // the parity's warps are past their reads of the other slot; this step's values
+                // (written a step ago) become visible; all eight warps leave together on an abort
+                if (group_sync_or(1 + g, 256, !ok)) { ok = false; break; }
+                stage_stats((i + 1) & 1, nx_l2, nx_dl);
+                fetch_stats(t + 4, nx_l2, nx_dl);
+            } else if (!ok) {
+                break;
             }
-            if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&bar_t[t & 1]), (t >> 1) & 1, ctl, kBwdBarT))) { ok = false; break; }
             tc_fence_after();
-            uint32_t sv[32], dv[32];
-            tmem_ld_x32(tb + half * 32, sv);                // both loads in flight, one wait
-            tmem_ld_x32(tb + kW + half * 32, dv);
-            tmem_ld32_arrive2(sv, dv);
             // masking only where the step touches the causal diagonal or the ragged end: masked
             // scores become -inf, so p = 0 and dS = 0
             const bool need_mask = (MODE == 0) ? (CAUSAL && c0 < (tile + 1) * kT)
                                                : ((CAUSAL && c0 + kW > tile * kT) || c0 + kW > seq_len);
-            if (need_mask) {
-#pragma unroll
-                for (int e = 0; e < 32; e++) {
-                    const int cg = c0 + half * 32 + e;      // global index of the streamed row
-                    const bool valid = (MODE == 0) ? (r_glob <= cg) : (cg < seq_len && (!CAUSAL || cg <= r_glob));
-                    sv[e] = valid ? sv[e] : 0xff800000u;    // -inf
-                }
-            }
             uint32_t pk[16], dk[16];
-            const uint64_t scale_log2_2 = pack2(scale_log2, scale_log2), scale2 = pack2(scale, scale);
-            const uint64_t row_neg_l2 = pack2(-row_lse2, -row_lse2), row_neg_dl = pack2(-row_delta * scale, -row_delta * scale);
 #pragma unroll
-            for (int e = 0; e < 32; e += 2) {
-                uint64_t neg_l2 = row_neg_l2, neg_dl = row_neg_dl;
-                if (MODE == 0) {                            // per column: one 16-byte shared load per pair
-                    const float4 st = *reinterpret_cast<const float4*>(st_neg[t & 1][half * 16 + (e >> 1)]);
-                    neg_l2 = pack2(st.x, st.y);
-                    neg_dl = pack2(st.z, st.w);
+            for (int c = 0; c < 2; c++) {                   // 16 columns of each product at a time
+                uint32_t sv[16], dv[16];
+                tmem_ld16x2_wait(tb + c * 16, sv, tb + kW + c * 16, dv);
+                if (c == 1 && !INPLACE) {
+                    // the product buffer is free for step t+2
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(smem_u32(&bar_tfree[g]));
                 }
-                // p = 2^(s * scale * log2e - lse * log2e);  dS = p * (dP * scale - delta * scale)
-                const uint64_t x = fma2(pack2(__uint_as_float(sv[e]), __uint_as_float(sv[e + 1])), scale_log2_2, neg_l2);
-                float x0, x1;
-                unpack2(x, x0, x1);
-                const float p0 = ex2_approx(x0), p1 = ex2_approx(x1);
-                const uint64_t g = fma2(pack2(__uint_as_float(dv[e]), __uint_as_float(dv[e + 1])), scale2, neg_dl);
-                float d0, d1;
-                unpack2(mul2(pack2(p0, p1), g), d0, d1);
-                pk[e >> 1] = pack_16<BF16>(p0, p1);
-                dk[e >> 1] = pack_16<BF16>(d0, d1);
+                if (need_mask) {
+#pragma unroll
+                    for (int e = 0; e < 16; e++) {
+                        const int cg = c0 + half * 32 + c * 16 + e;     // global index of the streamed row
+                        const bool valid = (MODE == 0) ? (r_glob <= cg) : (cg < seq_len && (!CAUSAL || cg <= r_glob));
+                        sv[e] = valid ? sv[e] : 0xff800000u;    // -inf
+                    }
+                }
+#pragma unroll
+                for (int e = 0; e < 16; e += 2) {
+                    uint64_t neg_l2 = row_neg_l2, neg_dl = row_neg_dl;
+                    if (MODE == 0) {                        // per column: one 16-byte shared load per pair
+                        const float4 st = *reinterpret_cast<const float4*>(st_neg[g][i & 1][half * 16 + c * 8 + (e >> 1)]);
+                        neg_l2 = pack2(st.x, st.y);
+                        neg_dl = pack2(st.z, st.w);
+                    }
+                    // p = 2^(s * scale * log2e - lse * log2e);  dS = p * (dP * scale - delta * scale)
+                    const uint64_t x = fma2(pack2(__uint_as_float(sv[e]), __uint_as_float(sv[e + 1])), scale_log2_2, neg_l2);
+                    float x0, x1;
+                    unpack2(x, x0, x1);
+                    const float p0 = ex2_approx(x0), p1 = ex2_approx(x1);
+                    const uint64_t gg = fma2(pack2(__uint_as_float(dv[e]), __uint_as_float(dv[e + 1])), scale2, neg_dl);
+                    float e0, e1;
+                    unpack2(mul2(pack2(p0, p1), gg), e0, e1);
+                    pk[c * 8 + (e >> 1)] = pack_16<BF16>(p0, p1);
+                    dk[c * 8 + (e >> 1)] = pack_16<BF16>(e0, e1);
+                }
             }
-            // in place: the 16 columns written here are the first half of the 32 this thread has read
-            if (MODE == 0) tmem_st_x16(tb + half * 32, pk);
-            tmem_st_x16(tb + kW + half * 32, dk);
+            if (!INPLACE && t >= 2) {
+                // the operand columns of this parity were read by the accumulations of step t-2
+                if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&bar_acc[(t - 2) % kStages]), ((t - 2) / kStages) & 1, ctl, kBwdBarAcc))) {
+                    ok = false;
+                    if (MODE == 0) continue;                // leave with the others at the next rendezvous
+                    break;
+                }
+            }
+            // each half writes its 16 columns of pairs; in place they land on the first half of the
+            // 32 columns this thread has read itself
+            const uint32_t op_off = INPLACE ? half * 32u : half * 16u;
+            if (MODE == 0) tmem_st_x16(tmem + lane_off + OPP0 + g * OP_STRIDE + op_off, pk);
+            tmem_st_x16(tmem + lane_off + OPD0 + g * OP_STRIDE + op_off, dk);
             tmem_wait_st();
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(&bar_p[t & 1]));
+            if (lane == 0) mbar_arrive(smem_u32(&bar_p[g]));
         }
         // ---- accumulators -> 16-bit -> global
         if (ok && __all_sync(0xffffffffu, mbar_wait(smem_u32(&bar_done), 0, ctl, kBwdBarDone))) {
             tc_fence_after();
 #pragma unroll 1
-            for (int which = 0; which < (MODE == 0 ? 2 : 1); which++) {
+            for (int which = 0; which < NACC; which++) {
                 uint16_t* dst = (which == 0 ? out0 : out1) + (static_cast<size_t>(bh) * seq_len + r_glob) * D;
                 const uint32_t acc = tmem + lane_off + (which == 0 ? ACC0_COL : ACC1_COL);
 #pragma unroll 1
-                for (int c = half * (D / 64); c < (half + 1) * (D / 64); c++) {
+                for (int c = (warp >> 2); c < D / 32; c += kComputeWarps / 4) {
                     uint32_t a[32];
                     tmem_ld32_wait(acc + c * 32, a);
                     if (r_glob < seq_len) {
@@ -375,7 +423,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap ta0, const __grid_constant__ CUte
     // completed and flushed, so that the end of this kernel implies the end of both.
     if (MODE == 1) asm volatile("griddepcontrol.wait;" ::: "memory");
     __syncthreads();
-    if (warp == kCtlWarp) tmem_dealloc(tmem, 512);
+    if (warp == kLoadWarp) tmem_dealloc(tmem, 512);
 }
 
 template <int D, bool CAUSAL, bool BF16, int MODE>

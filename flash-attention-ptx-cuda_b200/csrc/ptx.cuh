@@ -76,6 +76,19 @@ __device__ __forceinline__ bool mbar_try_wait_parked(uint32_t bar, uint32_t pari
     return ok != 0;
 }
 
+// Named barrier over `n_threads` threads that also ORs a flag: every participant gets the same
+// answer, so a group of warps leaves a loop together.
+__device__ __forceinline__ bool group_sync_or(int barrier, int n_threads, bool flag) {
+    uint32_t out;
+    asm volatile(
+        "{\n\t.reg .pred p, q;\n\t"
+        "setp.ne.u32 q, %3, 0;\n\t"
+        "bar.red.or.pred p, %1, %2, q;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(out) : "r"(barrier), "r"(n_threads), "r"(flag ? 1u : 0u) : "memory");
+    return out != 0;
+}
+
 // Shared per-CTA control block for the bounded waits.
 struct WaitCtl {
     volatile int* abort_flag;   // in shared memory: set by the first waiter that gives up
