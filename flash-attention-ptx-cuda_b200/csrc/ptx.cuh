@@ -165,6 +165,12 @@ __device__ __forceinline__ void tma_store_wait_read() {
 __device__ __forceinline__ void tma_store_wait_read_keep1() {
     asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
 }
+// One 32-byte store (address 32-byte aligned).
+__device__ __forceinline__ void st_global_v8(void* p, const uint32_t (&w)[8]) {
+    asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(p), "r"(w[0]), "r"(w[1]), "r"(w[2]),
+                 "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7]) : "memory");
+}
+
 // Orders generic-proxy shared-memory writes before later async-proxy (TMA) reads.
 __device__ __forceinline__ void fence_proxy_async_smem() {
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
