@@ -106,30 +106,38 @@ __host__ __device__ constexpr uint32_t op16_col(int kk, bool in_place) {
     return in_place ? (kk < 2 ? 0u : 32u) + (kk & 1) * 8u : kk * 8u;
 }
 
+// delta = rowsum(dO o O).  d_head / 8 lanes per row, 16 bytes of each tensor per lane: a warp
+// covers 4 rows (d_head 64) or 2 (d_head 128) with one load instruction per tensor.
 template <bool BF16>
 __global__ void delta_kernel(const uint16_t* __restrict__ o, const uint16_t* __restrict__ d_o,
                              float* __restrict__ delta, long long n_rows, int d_head) {
-    const long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    if (row >= n_rows) return;
+    const int lanes_per_row = d_head >> 3;                       // 8 or 16
+    const int rows_per_warp = 32 / lanes_per_row;
     const int lane = threadIdx.x & 31;
+    const long long warp_id = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const long long row = warp_id * rows_per_warp + lane / lanes_per_row;
+    const int c = (lane % lanes_per_row) * 8;
     float acc = 0.0f;
-    for (int c = lane * 2; c < d_head; c += 64) {
-        const uint32_t a = *reinterpret_cast<const uint32_t*>(o + row * d_head + c);
-        const uint32_t b = *reinterpret_cast<const uint32_t*>(d_o + row * d_head + c);
-        float a0, a1, b0, b1;
-        if constexpr (BF16) {
-            a0 = __uint_as_float(a << 16); a1 = __uint_as_float(a & 0xFFFF0000u);
-            b0 = __uint_as_float(b << 16); b1 = __uint_as_float(b & 0xFFFF0000u);
-        } else {
-            const float2 fa2 = __half22float2(*reinterpret_cast<const __half2*>(&a));
-            const float2 fb2 = __half22float2(*reinterpret_cast<const __half2*>(&b));
-            a0 = fa2.x; a1 = fa2.y; b0 = fb2.x; b1 = fb2.y;
-        }
-        acc = fmaf(a0, b0, fmaf(a1, b1, acc));
-    }
+    if (row < n_rows) {
+        const uint4 a = *reinterpret_cast<const uint4*>(o + row * d_head + c);
+        const uint4 b = *reinterpret_cast<const uint4*>(d_o + row * d_head + c);
+        const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {b.x, b.y, b.z, b.w};
 #pragma unroll
-    for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
-    if (lane == 0) delta[row] = acc;
+        for (int i = 0; i < 4; i++) {
+            float a0, a1, b0, b1;
+            if constexpr (BF16) {
+                a0 = __uint_as_float(aw[i] << 16); a1 = __uint_as_float(aw[i] & 0xFFFF0000u);
+                b0 = __uint_as_float(bw[i] << 16); b1 = __uint_as_float(bw[i] & 0xFFFF0000u);
+            } else {
+                const float2 fa2 = __half22float2(*reinterpret_cast<const __half2*>(&aw[i]));
+                const float2 fb2 = __half22float2(*reinterpret_cast<const __half2*>(&bw[i]));
+                a0 = fa2.x; a1 = fa2.y; b0 = fb2.x; b1 = fb2.y;
+            }
+            acc = fmaf(a0, b0, fmaf(a1, b1, acc));
+        }
+    }
+    for (int off = lanes_per_row >> 1; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+    if (row < n_rows && (lane % lanes_per_row) == 0) delta[row] = acc;
 }
 
 // One unit of work: one stationary tile of one head and the rows that stream past it.
@@ -653,7 +661,8 @@ FA_EXPORT int fa_backward(const fa_backward_args* a) {
     cudaStream_t stream = static_cast<cudaStream_t>(a->stream);
     const bool bf = a->dtype == FA_DTYPE_BF16;
     {
-        const unsigned blocks = (unsigned)((n_rows + 7) / 8);
+        const long long rows_per_block = 8 * (32 / (a->d_head >> 3));      // 8 warps of 4 or 2 rows
+        const unsigned blocks = (unsigned)((n_rows + rows_per_block - 1) / rows_per_block);
         if (bf) delta_kernel<true><<<blocks, 256, 0, stream>>>(static_cast<const uint16_t*>(a->o),
                     static_cast<const uint16_t*>(a->d_o), delta, n_rows, a->d_head);
         else    delta_kernel<false><<<blocks, 256, 0, stream>>>(static_cast<const uint16_t*>(a->o),
