@@ -207,9 +207,14 @@ bwd_kernel(const __grid_constant__ CUtensorMap ta0, const __grid_constant__ CUte
     //   bar_ostaged / bar_ofree[b] an item's output tiles staged in buffer b / read by their TMA store
     __shared__ __align__(8) uint64_t bar_a[2], bar_afree[2], bar_full[kStages], bar_acc[kStages], bar_t[2], bar_tfree[2],
         bar_p[2], bar_done, bar_accfree, bar_ostaged, bar_ofree[2];
-    // MODE 0: statistics of the streamed queries of a parity's current / next step, per column pair
-    // {-lse*log2e (col 0, col 1), -delta*scale (col 0, col 1)}: the addends of the two packed FMAs
-    __shared__ __align__(16) float st_neg[2][2][kW / 2][4];
+    // MODE 0: statistics of the streamed queries of the current / next step, per column pair
+    // {-lse*log2e (col 0, col 1), -delta*scale (col 0, col 1)}: the addends of the two packed FMAs.
+    // WARP_STATS: every compute warp stages the 32 columns it works on itself (lane j: column j), so
+    // a __syncwarp orders writes and reads and the warps of a parity need not meet.  Otherwise
+    // (d_head 128, where that measured 9 % slower) threads 0..63 of a parity stage its 64 columns
+    // and the parity's eight warps meet at a named barrier once per step.
+    constexpr bool WARP_STATS = !INPLACE;
+    __shared__ __align__(16) float st_neg[MODE != 0 ? 1 : (WARP_STATS ? kComputeWarps : 2)][2][WARP_STATS ? 16 : 32][4];
     __shared__ uint32_t tmem_slot;
     __shared__ int abort_flag;
 
@@ -379,6 +384,11 @@ bwd_kernel(const __grid_constant__ CUtensorMap ta0, const __grid_constant__ CUte
         const int g = warp >> 3;                            // parity of the steps this warp works on
         const int half = (warp >> 2) & 1;                   // which 32 streamed columns of a step
         const int gt = tid & 255;                           // thread within the parity's warps
+        // MODE 0: the streamed column of a step whose statistics this thread stages, and where
+        const int st_col = WARP_STATS ? half * 32 + lane : gt;
+        const bool st_mine = WARP_STATS || gt < kW;
+        const int st_set = (MODE != 0) ? 0 : (WARP_STATS ? warp : g);
+        const int st_pair = WARP_STATS ? (lane >> 1) : (gt >> 1) & 31, st_pair0 = WARP_STATS ? 0 : half * 16;
         const int r = tid & (kT - 1);                       // == TMEM lane
         const uint32_t lane_off = static_cast<uint32_t>((warp & 3) * 32) << 16;
         const float scale_log2 = scale * kLog2e;
@@ -390,8 +400,8 @@ bwd_kernel(const __grid_constant__ CUtensorMap ta0, const __grid_constant__ CUte
         // `ahead` = 1 (MODE 0 only): the parity's second step.
         auto prefetch = [&](const BwdItem& x, int gs_x, int ahead, float& l2, float& dl) {
             const int t = ((g ^ gs_x) & 1) + 2 * ahead;
-            const int row = (MODE == 1) ? x.tile * kT + r : x.row0 + t * kW + gt;
-            const bool mine = (MODE == 1) ? (ahead == 0) : (gt < kW && t < x.n_steps);
+            const int row = (MODE == 1) ? x.tile * kT + r : x.row0 + t * kW + st_col;
+            const bool mine = (MODE == 1) ? (ahead == 0) : (st_mine && t < x.n_steps);
             l2 = INFINITY;
             dl = 0.0f;
             if (mine && row < seq_len) {
@@ -418,13 +428,16 @@ bwd_kernel(const __grid_constant__ CUtensorMap ta0, const __grid_constant__ CUte
             // fetch those of its step after next from global memory and stage those of its next step in
             // shared memory while the current ones are in use; rows past the end get LSE = +inf
             auto fetch_stats = [&](int t, float& l2, float& dl) {
-                const int qi = row0 + t * kW + gt;
+                const int qi = row0 + t * kW + st_col;
                 l2 = INFINITY;
                 dl = 0.0f;
-                if (MODE == 0 && gt < kW && t < n_steps && qi < seq_len) { l2 = lse_h[qi] * kLog2e; dl = delta_h[qi]; }
+                if (MODE == 0 && st_mine && t < n_steps && qi < seq_len) { l2 = lse_h[qi] * kLog2e; dl = delta_h[qi]; }
             };
             auto stage_stats = [&](int slot, float l2, float dl) {
-                if (gt < kW) { st_neg[g][slot][gt >> 1][gt & 1] = -l2; st_neg[g][slot][gt >> 1][2 + (gt & 1)] = -dl * scale; }
+                if (st_mine) {
+                    st_neg[st_set][slot][st_pair][st_col & 1] = -l2;
+                    st_neg[st_set][slot][st_pair][2 + (st_col & 1)] = -dl * scale;
+                }
             };
             const int t_first = (g ^ gs) & 1;               // this parity's first step of the item
             float nx_l2, nx_dl;
@@ -440,14 +453,19 @@ bwd_kernel(const __grid_constant__ CUtensorMap ta0, const __grid_constant__ CUte
                 const int c0 = row0 + t * kW;               // first streamed row (= column of T0/T1) of the step
                 const uint32_t tb = tmem + lane_off + g * 128 + half * 32;
                 ok = ok && __all_sync(0xffffffffu, mbar_wait(smem_u32(&bar_t[g]), i & 1, ctl, kBwdBarT));
-                if (MODE == 0) {
+                if (MODE == 0 && !WARP_STATS) {
                     // the parity's warps are past their reads of the other slot; this step's values
                     // (written a step ago) become visible; all eight warps leave together on an abort
                     if (group_sync_or(1 + g, 256, !ok)) { ok = false; break; }
-                    stage_stats((i + 1) & 1, nx_l2, nx_dl);
-                    fetch_stats(t + 4, nx_l2, nx_dl);
                 } else if (!ok) {
                     break;
+                }
+                if (MODE == 0) {
+                    stage_stats((i + 1) & 1, nx_l2, nx_dl);
+                    // own staging: every lane is past its reads of that slot (the warp has synchronised
+                    // since), and this step's values, written a step ago, are visible from here
+                    if (WARP_STATS) __syncwarp();
+                    fetch_stats(t + 4, nx_l2, nx_dl);
                 }
                 tc_fence_after();
                 // masking only where the step touches the causal diagonal or the ragged end: masked
@@ -477,7 +495,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap ta0, const __grid_constant__ CUte
                     for (int e = 0; e < 16; e += 2) {
                         uint64_t neg_l2 = row_neg_l2, neg_dl = row_neg_dl;
                         if (MODE == 0) {                    // per column: one 16-byte shared load per pair
-                            const float4 st = *reinterpret_cast<const float4*>(st_neg[g][i & 1][half * 16 + c * 8 + (e >> 1)]);
+                            const float4 st = *reinterpret_cast<const float4*>(st_neg[st_set][i & 1][st_pair0 + c * 8 + (e >> 1)]);
                             neg_l2 = pack2(st.x, st.y);
                             neg_dl = pack2(st.z, st.w);
                         }
@@ -497,7 +515,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap ta0, const __grid_constant__ CUte
                     // the operand columns of this parity were read by the accumulations of step T-2
                     if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&bar_acc[(T - 2) % kStages]), ((T - 2) / kStages) & 1, ctl, kBwdBarAcc))) {
                         ok = false;
-                        if (MODE == 0) continue;            // leave with the others at the next rendezvous
+                        if (MODE == 0 && !WARP_STATS) continue;   // leave with the others at the next rendezvous
                         break;
                     }
                 }
@@ -511,7 +529,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap ta0, const __grid_constant__ CUte
                 __syncwarp();
                 if (lane == 0) mbar_arrive(smem_u32(&bar_p[g]));
             }
-            if (!ok && MODE == 1) break;
+            if (!ok && (MODE == 1 || WARP_STATS)) break;
             BwdItem nx;
             const bool have_nx = bwd_item<CAUSAL, MODE>(k + 1, n_items, n_bh, n_tiles, seq_len, nx);
             if (have_nx) {
