@@ -57,6 +57,29 @@ def test_backward_matches_autograd(fa, dev, dtype, causal, bh, s, d):
         assert err < rel * r.abs().max().item() + ab, (name, err, r.abs().max().item())
 
 
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("bh,s,d,dtype", [(300, 192, 64, "f16"), (500, 64, 64, "f16"), (450, 320, 64, "bf16"),
+                                          (200, 192, 128, "f16"), (330, 100, 128, "bf16")])
+def test_backward_many_items_per_cta(fa, dev, causal, bh, s, d, dtype):
+    """More (tile, head) work items than SMs, with odd step counts per item: every persistent CTA
+    walks several items, so the step parity, the ring positions and the stationary-tile buffers
+    carry over from one item to the next, some items give one of the two step parities nothing to
+    do, and outputs are staged and stored while the next item runs."""
+    g = torch.Generator().manual_seed(4000 + bh + s + d)
+    q, k, v, d_o = (torch.randn((bh, s, d), generator=g).to(TD[dtype]) for _ in range(4))
+    scale = 1.0 / np.sqrt(d)
+    ref = autograd_reference(q, k, v, d_o, scale, causal)
+    got = run_backward(fa, dev, q, k, v, d_o, scale, causal, dtype)
+    rel, ab = TOL[dtype]
+    for name, r, x in zip(("dQ", "dK", "dV"), ref, got):
+        assert torch.isfinite(x).all(), name
+        # per head, so that one wrong item cannot hide behind the largest entry of another head
+        err = (x - r).abs().amax(dim=(1, 2))
+        bound = rel * r.abs().amax(dim=(1, 2)) + ab
+        bad = torch.nonzero(err > bound).flatten().tolist()
+        assert not bad, (name, bad[:8], err.max().item())
+
+
 def test_backward_argument_errors(fa, dev):
     t = torch.zeros(128 * 64, device=dev, dtype=torch.float16)
     l = torch.zeros(128, device=dev, dtype=torch.float32)
