@@ -65,12 +65,12 @@ namespace fa {
 namespace {
 
 constexpr int kT = 128;                  // tile edge: stationary rows per CTA
-constexpr int kBwdThreads = 768;         // 24 warps (21-23 idle: register pools move by groups of four warps)
+constexpr int kBwdThreads = 768;         // 24 warps (22, 23 idle: register pools move by groups of four warps)
 constexpr int kComputeWarps = 16;
 constexpr int kProdWarp = 16;            // 16, 17: product MMAs of even / odd steps
 constexpr int kAccWarp = 18;             // 18, 19: accumulating MMAs, one accumulator each
 constexpr int kLoadWarp = 20;            // TMA loads
-constexpr int kTmemWarp = 21;            // TMEM allocation and release
+constexpr int kTmemWarp = 21;            // TMEM allocation and release; TMA stores of staged output tiles
 constexpr int kW = 64;                   // streamed rows per step (columns of one product)
 constexpr float kLog2e = 1.4426950408889634f;
 // setmaxnreg moves registers inside the pool the CTA got at launch (threads x registers at launch)
