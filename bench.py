@@ -602,7 +602,7 @@ def run_other_configs(fa, torch, dev, stream, peaks, gqa_batch=0):
     tf = causal_flops(bh, s, d) / (ms * 1e-3) / 1e12
     out["e4m3_b8_h16_s4096_d128_causal"] = {"ms": ms, "tflops": tf,
                                             "frac_of_measured_bf16_peak": tf / peaks["tflops"],
-                                            "note": "Q K^T on the 8-bit kind, P V on the 16-bit kind"}
+                                            "note": "Q K^T on the 8-bit kind, P V on the 16-bit kind from an fp16 copy of V made by a pre-pass inside the call"}
     del q8, k8, v8, o, lse
 
     # backward pass (dQ, dK, dV) on config 2's shape; 2.5x the forward's FLOP (5 products against 2)

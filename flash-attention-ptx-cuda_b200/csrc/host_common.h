@@ -32,6 +32,11 @@ struct DeviceState {
     cudaStream_t pipe[3] = {};      // host-entry streams: chunks of heads are copied in, computed
                                     // and copied out on alternating streams so the two PCIe
                                     // directions and the kernels overlap
+    // e4m3 prefill: memory pool of the library's own for the stream-ordered fp16 copy of V (created
+    // at the first such call; keeps what it has allocated, so later calls allocate nothing new)
+    std::atomic<bool> pool_ready{false};
+    std::mutex pool_mutex;
+    cudaMemPool_t scratch_pool = nullptr;
 };
 
 // State of the current device (created on first use).  nullptr on CUDA failure.

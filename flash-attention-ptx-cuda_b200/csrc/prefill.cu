@@ -91,7 +91,7 @@ __device__ __forceinline__ uint32_t e4m3x2_to_f16x2(uint16_t v) {
 }
 
 
-template <int D, bool FP8>
+template <int D, bool FP8, bool V8 = FP8>
 struct PrefillSmem {
     static constexpr int kNBox    = D / 64;               // 64-column (128-byte) boxes per 16-bit row
     static constexpr int kBox     = 128 * 128;            // one box: 128 rows x 128 bytes
@@ -99,11 +99,11 @@ struct PrefillSmem {
     static constexpr int kQBytes  = FP8 ? kBox : kNBox * kBox;
     static constexpr int kKBytes  = kQBytes;
     static constexpr int kVBytes  = kNBox * kBox;         // 16-bit V operand of P V (e4m3: converted copy)
-    static constexpr int kV8Bytes = FP8 ? kBox : 0;       // landing buffers of the e4m3 V tiles
+    static constexpr int kV8Bytes = V8 ? kBox : 0;       // landing buffers of the e4m3 V tiles
     static constexpr int kOBytes  = kNBox * kBox;         // epilogue staging (16-bit output tile)
     static constexpr int NK  = (D == 64) ? 4 : 2;
-    static constexpr int NV  = (D == 64) ? 4 : (FP8 ? 3 : 2);   // e4m3: the converted (fp16) V tiles
-    static constexpr int NV8 = FP8 ? 2 : 0;
+    static constexpr int NV  = (D == 64) ? 4 : (V8 ? 3 : 2);   // e4m3: the converted (fp16) V tiles
+    static constexpr int NV8 = V8 ? 2 : 0;
     static constexpr int kTotal = kQBytes + NK * kKBytes + NV * kVBytes + NV8 * kV8Bytes + kOBytes + 1024;
 };
 
@@ -193,8 +193,11 @@ __device__ __forceinline__ bool get_item(int k, int n_items, int n_bh, int n_qti
 }
 
 // FP8: Q, K, V are e4m3 codes with per-head scales.  S = Q K^T runs on the 8-bit tensor-core
-// kind; V is converted e4m3 -> fp16 in shared memory by warps 10-11 (exact) and P V runs on the
-// 16-bit kind with P in fp16, because an e4m3 P (3 mantissa bits) misses the output tolerance.
+// kind; P V runs on the 16-bit kind with P in fp16, because an e4m3 P (3 mantissa bits) misses
+// the output tolerance, so V has to be fp16 as well (exact).  Prefill gets it from a pre-pass
+// over the whole tensor (e4m3_to_f16_kernel) and loads it like any 16-bit V; decode over an
+// e4m3 cache (GQA) cannot rewrite the cache, so there the e4m3 V tiles land in buffers of
+// their own and warps 12-15 convert each one in shared memory (V8).
 // The Q and K scales fold into the softmax scale, the V scale into the final normalisation;
 // the output is bf16.
 template <int D, bool CAUSAL, bool BF16, bool FP8, bool GQA, bool GROUPED>
@@ -207,7 +210,8 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                const GqaDev gq) {
     static_assert(!FP8 || (D == 128 && BF16), "e4m3 variant: d_head 128, bf16 output");
     static_assert(!GQA || !CAUSAL, "grouped-query decode: one query row per head, every key visible");
-    using L = PrefillSmem<D, FP8>;
+    constexpr bool V8 = FP8 && GQA;                       // V arrives as e4m3 and is converted in shared memory
+    using L = PrefillSmem<D, FP8, V8>;
     constexpr int NBOX = L::kNBox, NK = L::NK, NV = L::NV;
     constexpr uint32_t O_COL = kNU * 128;
     static_assert(NK <= kRing && NV <= kRing && kNU <= kRing, "a ring entry must not be reused before its waiters have looked");
@@ -249,7 +253,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         mbar_init(smem_u32(&bar_ofree), 4);              // the epilogue warps have read O
         mbar_init(smem_u32(&bar_odone), 1);
         for (int i = 0; i < NK; i++) mbar_init(smem_u32(&bar_kf[i]), 1);
-        for (int i = 0; i < NV; i++) mbar_init(smem_u32(&bar_vf[i]), FP8 ? 128 : 1);
+        for (int i = 0; i < NV; i++) mbar_init(smem_u32(&bar_vf[i]), V8 ? 128 : 1);
         for (int i = 0; i < kRing; i++) { mbar_init(smem_u32(&bar_qk[i]), 1); mbar_init(smem_u32(&bar_pvd[i]), 1); }
         for (int i = 0; i < kNU; i++) mbar_init(smem_u32(&bar_pf[i]), 4);   // one arrival per warp of the owning group
         for (int i = 0; i < 2; i++) {
@@ -357,7 +361,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                 Item it;
                 if (!get_item<CAUSAL, GQA, GROUPED>(r, n_items, n_bh, n_qtiles, seq_len, gq, it)) continue;
                 for (int j = 0; j < it.n_kv; j++, g++) {
-                    if constexpr (FP8) {
+                    if constexpr (V8) {
                         // e4m3 V lands in its own buffers; warps 12-15 turn it into the fp16 operand.
                         const int s8 = g & 1;
                         if (g >= 2 && !mbar_wait(smem_u32(&bar_v8e[s8]), ((g >> 1) - 1) & 1, ctl, kBarV8Empty)) { ok = false; break; }
@@ -520,7 +524,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                 }
                 continue;
             }
-            if constexpr (FP8) {
+            if constexpr (V8) {
                 // ---- e4m3 -> fp16 conversion of the item's V tiles (exact)
                 for (int j = 0; j < it.n_kv; j++, g++) {
                     const int s8 = g & 1, sv = g % NV;
@@ -854,7 +858,7 @@ int heads_per_group(int n_bh, int seq_len, int d_head, int elem_bytes) {
 template <int D, bool CAUSAL, bool BF16, bool FP8>
 int launch_instance(const fa_prefill_args& a, DeviceState* st, const CUtensorMap& tq,
                     const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& to) {
-    using L = PrefillSmem<D, FP8>;
+    using L = PrefillSmem<D, FP8, false>;
     const int n_bh = a.batch_size * a.num_heads;
     GqaDev order{};
     order.group = heads_per_group(n_bh, a.seq_len, a.d_head, FP8 ? 1 : 2);
@@ -970,17 +974,83 @@ int launch_decode_gqa(const GqaLaunch& g, DeviceState* st) {
 }
 
 
-// e4m3 inputs (d_head 128), bf16 output.
+// e4m3 codes -> fp16 (exact), 16 codes per thread.
+__global__ void e4m3_to_f16_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst, long long n16) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n16) return;
+    const uint4 c = src[i];
+    const uint32_t w[4] = {c.x, c.y, c.z, c.w};
+    uint4 lo, hi;
+    lo.x = e4m3x2_to_f16x2(static_cast<uint16_t>(w[0] & 0xFFFFu)); lo.y = e4m3x2_to_f16x2(static_cast<uint16_t>(w[0] >> 16));
+    lo.z = e4m3x2_to_f16x2(static_cast<uint16_t>(w[1] & 0xFFFFu)); lo.w = e4m3x2_to_f16x2(static_cast<uint16_t>(w[1] >> 16));
+    hi.x = e4m3x2_to_f16x2(static_cast<uint16_t>(w[2] & 0xFFFFu)); hi.y = e4m3x2_to_f16x2(static_cast<uint16_t>(w[2] >> 16));
+    hi.z = e4m3x2_to_f16x2(static_cast<uint16_t>(w[3] & 0xFFFFu)); hi.w = e4m3x2_to_f16x2(static_cast<uint16_t>(w[3] >> 16));
+    dst[2 * i] = lo;
+    dst[2 * i + 1] = hi;
+}
+
+// e4m3 inputs (d_head 128), bf16 output.  V is converted to fp16 once, into a stream-ordered
+// scratch allocation (cudaMallocFromPoolAsync / cudaFreeAsync on the caller's stream) that lives
+// for the call (converting every V tile in shared memory inside the
+// kernel made this path slower than bf16: 0.57 against 0.44 ms on B=8 H=16 S=4096 causal); heads
+// are taken in chunks so that the scratch stays below kFp8ScratchBytes.
+constexpr size_t kFp8ScratchBytes = 256ull << 20;
 int launch_prefill_fp8(const fa_prefill_args& a, DeviceState* st) {
     const uint64_t n_bh = (uint64_t)a.batch_size * a.num_heads;
-    CUtensorMap tq, tk, tv, to;
-    int rc;
-    if ((rc = make_tensor_map_3d(&tq, a.q, FA_DTYPE_E4M3, 128, a.seq_len, n_bh, 128, kBM)) != FA_OK) return rc;
-    if ((rc = make_tensor_map_3d(&tk, a.k, FA_DTYPE_E4M3, 128, a.seq_len, n_bh, 128, kBN)) != FA_OK) return rc;
-    if ((rc = make_tensor_map_3d(&tv, a.v, FA_DTYPE_E4M3, 128, a.seq_len, n_bh, 128, kBN)) != FA_OK) return rc;
-    if ((rc = make_tensor_map_3d(&to, a.o, FA_DTYPE_BF16, 128, a.seq_len, n_bh, 64, kBM)) != FA_OK) return rc;
-    if (a.causal) return launch_instance<128, true, true, true>(a, st, tq, tk, tv, to);
-    return launch_instance<128, false, true, true>(a, st, tq, tk, tv, to);
+    const size_t head_elems = (size_t)a.seq_len * 128;             // per head and tensor
+    uint64_t chunk = kFp8ScratchBytes / (head_elems * 2);
+    if (chunk < 1) chunk = 1;
+    if (chunk > n_bh) chunk = n_bh;
+    cudaStream_t stream = static_cast<cudaStream_t>(a.stream);
+    // The scratch comes from a pool of the library's own whose release threshold is unlimited: the
+    // process's default pool would hand the memory back at every synchronisation and the next call
+    // would pay for a fresh allocation (measured: 4 ms on the first call after a synchronise).
+    if (!st->pool_ready.load(std::memory_order_acquire)) {
+        std::lock_guard<std::mutex> lock(st->pool_mutex);
+        if (!st->pool_ready.load(std::memory_order_relaxed)) {
+            cudaMemPoolProps props = {};
+            props.allocType = cudaMemAllocationTypePinned;
+            props.handleTypes = cudaMemHandleTypeNone;
+            props.location.type = cudaMemLocationTypeDevice;
+            props.location.id = st->device;
+            FA_CUDA_TRY(cudaMemPoolCreate(&st->scratch_pool, &props));
+            uint64_t keep = UINT64_MAX;
+            FA_CUDA_TRY(cudaMemPoolSetAttribute(st->scratch_pool, cudaMemPoolAttrReleaseThreshold, &keep));
+            st->pool_ready.store(true, std::memory_order_release);
+        }
+    }
+    void* v16 = nullptr;
+    FA_CUDA_TRY(cudaMallocFromPoolAsync(&v16, chunk * head_elems * 2, st->scratch_pool, stream));
+    int rc = FA_OK;
+    for (uint64_t h0 = 0; h0 < n_bh && rc == FA_OK; h0 += chunk) {
+        const uint64_t nh = (n_bh - h0 < chunk) ? n_bh - h0 : chunk;
+        // this chunk's heads as a problem of its own: batch 1 x nh heads
+        fa_prefill_args c = a;
+        c.batch_size = 1;
+        c.num_heads = (int)nh;
+        c.q = static_cast<const uint8_t*>(a.q) + h0 * head_elems;
+        c.k = static_cast<const uint8_t*>(a.k) + h0 * head_elems;
+        c.v = static_cast<const uint8_t*>(a.v) + h0 * head_elems;
+        c.o = static_cast<uint16_t*>(a.o) + h0 * head_elems;
+        if (a.lse) c.lse = a.lse + h0 * a.seq_len;
+        c.q_scale = a.q_scale + h0;
+        c.k_scale = a.k_scale + h0;
+        c.v_scale = a.v_scale + h0;
+        const long long n16 = (long long)(nh * head_elems / 16);
+        e4m3_to_f16_kernel<<<(unsigned)((n16 + 255) / 256), 256, 0, stream>>>(static_cast<const uint4*>(c.v),
+                                                                            static_cast<uint4*>(v16), n16);
+        if (cudaGetLastError() != cudaSuccess) { rc = FA_ERR_CUDA; break; }
+        CUtensorMap tq, tk, tv, to;
+        if ((rc = make_tensor_map_3d(&tq, c.q, FA_DTYPE_E4M3, 128, a.seq_len, nh, 128, kBM)) != FA_OK) break;
+        if ((rc = make_tensor_map_3d(&tk, c.k, FA_DTYPE_E4M3, 128, a.seq_len, nh, 128, kBN)) != FA_OK) break;
+        if ((rc = make_tensor_map_3d(&tv, v16, FA_DTYPE_F16, 128, a.seq_len, nh, 64, kBN)) != FA_OK) break;
+        if ((rc = make_tensor_map_3d(&to, c.o, FA_DTYPE_BF16, 128, a.seq_len, nh, 64, kBM)) != FA_OK) break;
+        rc = a.causal ? launch_instance<128, true, true, true>(c, st, tq, tk, tv, to)
+                      : launch_instance<128, false, true, true>(c, st, tq, tk, tv, to);
+    }
+    const cudaError_t fe = cudaFreeAsync(v16, stream);            // after the last kernel that reads it, in stream order
+    if (rc == FA_OK && fe != cudaSuccess) rc = FA_ERR_CUDA;
+    return rc;
 }
 
 }  // namespace fa

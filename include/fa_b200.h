@@ -52,6 +52,12 @@ enum { FA_DTYPE_F16 = 0, FA_DTYPE_BF16 = 1, FA_DTYPE_E4M3 = 2 };
  * dtype E4M3: q,k,v e4m3 codes with per-(batch*head) dequantisation scales
  *             q_scale,k_scale,v_scale (device, fp32, [batch_size*num_heads],
  *             value = code * scale); o bf16.
+ *             The call first writes an fp16 copy of v (P V runs on the 16-bit
+ *             tensor-core kind) into scratch memory that it takes, in stream
+ *             order, from a memory pool of the library's own and returns the same
+ *             way (cudaMallocFromPoolAsync / cudaFreeAsync on args->stream): at
+ *             most 256 MB, heads processed in chunks beyond that; the pool keeps
+ *             the memory, so only the first call per device allocates.
  * d_head 64 or 128 (E4M3: 128 only).  seq_len any positive value.
  */
 typedef struct fa_prefill_args {
