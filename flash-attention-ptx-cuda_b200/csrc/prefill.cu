@@ -44,8 +44,9 @@
 //   warps 12-15        epilogue of every item, one thread per query row: combine the two
 //                      partial sums, O / l -> 16-bit -> swizzled staging -> TMA store
 //                      (clipped per head); LSE as fp32.  The tensor pipe and the softmax
-//                      already work on the next item meanwhile.  For e4m3 inputs the same
-//                      warps first turn each V tile into the fp16 operand of P V.
+//                      already work on the next item meanwhile.  In decode over an e4m3
+//                      cache the same warps first turn each V tile into the fp16 operand
+//                      of P V (the e4m3 prefill gets an fp16 V from a pre-pass instead).
 //
 // TMEM (all 512 columns): three score buffers [0,128) [128,256) [256,384), O [384,384+D).
 #include <atomic>
@@ -492,8 +493,8 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         // ------------------------------------------------------------ helper warps 12-15
         // Epilogue of every item, one thread per query row: combine the two softmax threads'
         // (max, sum), read the row of O from TMEM, normalise, stage in swizzled shared memory,
-        // TMA-store; the softmax warps are already on the next item.  For e4m3 inputs the same
-        // warps first turn each V tile of the item into the fp16 operand of P V.
+        // TMA-store; the softmax warps are already on the next item.  In decode over an e4m3 cache
+        // (V8) the same warps first turn each V tile of the item into the fp16 operand of P V.
         const int ct = tid - 384;                         // 0..127
         const int r_in_tile = ct;                         // == TMEM lane: (warp & 3) * 32 + lane
         const uint32_t t_o = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16) + O_COL;
