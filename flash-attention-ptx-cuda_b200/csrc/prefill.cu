@@ -182,6 +182,11 @@ __device__ __forceinline__ bool get_item(int k, int n_items, int n_bh, int n_qti
         const int h0 = gi * gq.group, hin = min(gq.group, n_bh - h0);
         qrank = rem / hin;
         it.bh = h0 + rem - qrank * hin;
+        // Under the causal mask every group runs from its heaviest to its lightest tiles, a sawtooth
+        // that the boustrophedon deal balances poorly (per-CTA totals up to 6 % above the mean on 32
+        // heads of 64 tiles); odd groups run light to heavy instead, which halves that (a CTA's total
+        // does not depend on the order in which it meets its items).
+        if (CAUSAL && (gi & 1)) qrank = n_qtiles - 1 - qrank;
     } else {
         qrank = idx / n_bh;
         it.bh = idx % n_bh;
